@@ -6,8 +6,8 @@ The reference holds one sequence in one contiguous fp32 cache sized at start
 batch of requests needs instead.
 
 Storages and groups.  The model says, per cache storage, what it needs
-(`PagedKVNeed` or `StateNeed`, or nothing).  Paged storages with the same
-(kv_heads, head_dim, window) form a *group*: one page pool, one block table per
+(`PagedKVNeed` or `StateNeed`, a `CompositeNeed` of several, or nothing).  Paged storages with the same
+(kv_heads, head_dim, window, chunk) form a *group*: one page pool, one block table per
 request, and a K and a V tensor `[num_pages, kv_heads, page_size, head_dim]` per
 storage (V with `v_head_dim` where a need gives one), all indexed by the group's page ids.  Groups with different needs (all
 keys / a window of keys, other head shapes) have pools and tables of their own.
@@ -28,7 +28,7 @@ from typing import Dict, List, Sequence, Tuple
 import numpy as np
 import torch
 
-from ..parts.base import PagedKVNeed, StateNeed
+from ..parts.base import CompositeNeed, PagedKVNeed, StateNeed
 from .pool import OutOfPages, PoolError, UnitPool
 
 NO_PAGE = -1
@@ -50,6 +50,12 @@ class StateStorage:
     shape: Tuple[int, ...]
     state: torch.Tensor | None = None
     fill: float = 0.0            # what a request's state holds when the request gets its slot
+
+
+@dataclass
+class CompositeStorage:
+    """The storages of a mixer with several needs, in the order of its `CompositeNeed`."""
+    parts: List[object]
 
 
 @dataclass
@@ -98,31 +104,47 @@ class CacheManager:
         # for tests: set `owners` to a dict and every hand-out of a page is logged there as
         # (group, page) -> [request ids in the order they held it]
         self.owners: Dict[tuple, list] | None = None
-        keys: Dict[PagedKVNeed, int] = {}
+        self._group_of: Dict[PagedKVNeed, int] = {}
         for i, need in enumerate(needs):
-            if need is None:
-                self.storages.append(None)
-            elif isinstance(need, PagedKVNeed):
-                if need not in keys:
-                    keys[need] = len(self.groups)
-                    self.groups.append(PagedGroup(need, UnitPool(self.num_pages, "page")))
-                g = keys[need]
-                self.groups[g].storages.append(i)
-                st = PagedStorage(g, self.page_size, need.window)
-                if device is not None:
-                    shape = (self.num_pages, need.kv_heads, self.page_size, need.head_dim)
-                    st.k_pages = torch.empty(shape, dtype=dtype, device=device)
-                    st.v_pages = torch.empty(shape[:3] + (need.v_head_dim or need.head_dim,), dtype=dtype, device=device)
-                self.storages.append(st)
-            elif isinstance(need, StateNeed):
-                self.has_state = True
-                st = StateStorage(tuple(need.shape), fill=float(need.fill))
-                if device is not None:
-                    st.state = torch.full((self.max_requests,) + tuple(need.shape), float(need.fill),
-                                          dtype=getattr(torch, need.dtype), device=device)
-                self.storages.append(st)
-            else:
-                raise TypeError(f"storage {i}: unknown cache need {need!r}")
+            self.storages.append(self._make_storage(i, need))
+
+    def _make_storage(self, i: int, need):
+        dtype, device = self.dtype, self.device
+        if need is None:
+            return None
+        if isinstance(need, CompositeNeed):
+            return CompositeStorage([self._make_storage(i, n) for n in need.parts])
+        if isinstance(need, PagedKVNeed):
+            if need not in self._group_of:
+                self._group_of[need] = len(self.groups)
+                self.groups.append(PagedGroup(need, UnitPool(self.num_pages, "page")))
+            g = self._group_of[need]
+            self.groups[g].storages.append(i)
+            st = PagedStorage(g, self.page_size, need.window)
+            if device is not None:
+                shape = (self.num_pages, need.kv_heads, self.page_size, need.head_dim)
+                st.k_pages = torch.empty(shape, dtype=dtype, device=device)
+                st.v_pages = torch.empty(shape[:3] + (need.v_head_dim or need.head_dim,), dtype=dtype, device=device)
+            return st
+        if isinstance(need, StateNeed):
+            self.has_state = True
+            st = StateStorage(tuple(need.shape), fill=float(need.fill))
+            if device is not None:
+                st.state = torch.full((self.max_requests,) + tuple(need.shape), float(need.fill),
+                                      dtype=getattr(torch, need.dtype), device=device)
+            return st
+        raise TypeError(f"storage {i}: unknown cache need {need!r}")
+
+    def leaf_storages(self):
+        """Every paged or state storage, those inside composite storages included."""
+        def walk(st):
+            if isinstance(st, CompositeStorage):
+                for part in st.parts:
+                    yield from walk(part)
+            elif st is not None:
+                yield st
+        for st in self.storages:
+            yield from walk(st)
 
     # ---- a request's life ----------------------------------------------------
     def open(self, request_id) -> RequestCache:
@@ -131,7 +153,7 @@ class CacheManager:
         slot = self.slots.take(1)[0]          # every request has a slot number, state or not
         rc = RequestCache(request_id, tables=[[] for _ in self.groups], slot=slot)
         if self.device is not None:
-            for st in self.storages:
+            for st in self.leaf_storages():
                 if isinstance(st, StateStorage):
                     st.state[slot].fill_(st.fill)
         self.live[request_id] = rc
@@ -182,10 +204,13 @@ class CacheManager:
         rc.n_tokens += n_new
         rc.reserved -= n_new
         for g, table in zip(self.groups, rc.tables):
-            w = g.need.window
-            if w is None:
+            w, c = g.need.window, g.need.chunk
+            if w is None and c is None:
                 continue
-            first_needed = rc.n_tokens - w + 1          # oldest key the next token sees
+            # oldest key the next token (at position n_tokens) sees: the window's first, or its chunk's first
+            first_needed = rc.n_tokens - w + 1 if w is not None else 0
+            if c is not None:
+                first_needed = max(first_needed, rc.n_tokens // c * c)
             b = 0
             while (b + 1) * self.page_size <= first_needed and b < len(table):
                 if table[b] != NO_PAGE:

@@ -109,7 +109,10 @@ def read_config_json(model_dir: str) -> dict:
 
 
 def architecture_name(raw: dict, where: str = "config.json") -> str:
-    """The model class name that config.json asks for (`architectures[0]`)."""
+    """The model class name that config.json asks for: `architectures[0]`, or the string under
+    `architecture` in a config.json that names its design that way."""
+    if "architectures" not in raw and isinstance(raw.get("architecture"), str):
+        return raw["architecture"]
     archs = raw.get("architectures")
     if not isinstance(archs, list) or len(archs) < 1 or not isinstance(archs[0], str):
         raise ConfigError(f"{where}: key 'architectures' must be a list with the model class name")

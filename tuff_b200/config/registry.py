@@ -19,6 +19,9 @@ class Architecture:
     parse_config: Callable[[dict, str], Any]       # raw config.json dict, where -> typed configuration
     model_spec: Callable[[Any], Any]               # typed configuration -> ModelSpec
     config_to_dict: Callable[[Any], dict]          # typed configuration -> config.json dict
+    # (typed configuration, checkpoint tensor name -> shape) -> typed configuration, for a design some of
+    # whose sizes only the tensors' shapes give; None: config.json gives them all
+    refine_config: Callable[[Any, dict], Any] | None = None
 
 
 _ARCHITECTURES: Dict[str, Architecture] = {}
@@ -51,13 +54,27 @@ def config_from_dict(raw: dict, where: str = "config.json"):
 
 def load_config(model_dir: str):
     raw = read_config_json(model_dir)
-    return config_from_dict(raw, f"{model_dir}/config.json")
+    arch, cfg = config_from_dict(raw, f"{model_dir}/config.json")
+    if arch.refine_config is not None:
+        from ..weights.safetensors_io import ModelFiles, SafetensorsError
+        try:
+            files = ModelFiles(model_dir)
+        except (SafetensorsError, OSError):
+            return arch, cfg              # no readable checkpoint: the loader will say so
+        try:
+            cfg = arch.refine_config(cfg, {n: tuple(e.shape) for n, e in files.entries.items()})
+        finally:
+            files.close()
+    return arch, cfg
 
 
 def _register_builtin() -> None:
     from ..models.lfm2 import lfm2_spec
     from .lfm2 import ARCHITECTURE, Lfm2Config
     register_architecture(Architecture(ARCHITECTURE, Lfm2Config.from_dict, lfm2_spec, lambda c: c.to_dict()))
+    from ..models.koridra import koridra_spec, refine_config
+    from .koridra import ARCHITECTURE as KORIDRA, KoridraConfig
+    register_architecture(Architecture(KORIDRA, KoridraConfig.from_dict, koridra_spec, lambda c: c.to_dict(), refine_config))
 
 
 _register_builtin()

@@ -9,6 +9,14 @@
 //                             query heads sharing a key/value head
 //                             (reference: src/lfm25_gpu.cu:506-578)
 //
+// Options beside the reference's form, all parameters: the rotation may pair neighbouring elements
+// (2i, 2i+1) instead of (i, i + span/2) and scale cos and sin by an amplitude; the norm may run over
+// a token's whole q (and whole k) projection instead of per head, with a weight per column
+// (`tuff_qk_sumsq` prepares the two sums per token); the values may be the keys as projected, before
+// norm and rotation (no value heads in qkv then); a query may see only the keys of its own chunk of
+// positions; the softmax may have a sink (a further score with no value) in its denominator; the
+// output may be scaled.
+//
 // The reference keeps one contiguous fp32 cache per sequence and is written for
 // head size 64; here the cache is paged ([page][kv_head][slot][hd], looked up
 // through a block table per batch row), the head size is any value up to 256,
@@ -35,7 +43,8 @@ qk_norm_rope_write_kernel(T* __restrict__ qkv, const float* __restrict__ q_norm_
                           const int* __restrict__ positions, const int* __restrict__ row_of_token,
                           const int* __restrict__ block_table, int max_blocks,
                           T* __restrict__ k_pages, T* __restrict__ v_pages,
-                          int H, int G, int hd, int rot_dim, int page_size, float eps, int write_kv, Bounds bounds) {
+                          int H, int G, int hd, int rot_dim, int page_size, float eps, int write_kv, Bounds bounds,
+                          int interleaved, float amplitude, const float* __restrict__ row_sumsq, int v_from_k) {
     constexpr int UNROLL = 4;                        // heads in flight per warp
     const int t = blockIdx.x;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -43,9 +52,17 @@ qk_norm_rope_write_kernel(T* __restrict__ qkv, const float* __restrict__ q_norm_
     pdl_launch_dependents();
     const int pos = ld_act(positions + t);
     const int r = ld_act(row_of_token + t);
-    const int n_heads = H + 2 * G;
+    const int n_heads = H + (v_from_k ? G : 2 * G);
     const int half = rot_dim >> 1, n_pairs = hd >> 1;
     T* base = qkv + (size_t)t * n_heads * hd;
+    // a norm over the whole projection: one scale for all q heads and one for all k heads of the token,
+    // and a weight per column of the projection instead of per element of a head
+    const int w_stride = row_sumsq ? hd : 0;
+    float whole_q = 1.f, whole_k = 1.f;
+    if (row_sumsq) {
+        whole_q = rsqrtf(ld_act(row_sumsq + 2 * (size_t)t) / (float)(H * hd) + eps);
+        whole_k = rsqrtf(ld_act(row_sumsq + 2 * (size_t)t + 1) / (float)(G * hd) + eps);
+    }
     size_t page_base = 0;
     int in_page = 0;
     if (write_kv) {
@@ -67,11 +84,14 @@ qk_norm_rope_write_kernel(T* __restrict__ qkv, const float* __restrict__ q_norm_
 #pragma unroll
     for (int i = 0; i < PPL; ++i) {
         const int j = lane + 32 * i;
-        e1[i] = j < half ? j : rot_dim + 2 * (j - half);
-        e2[i] = j < half ? j + half : e1[i] + 1;
+        e1[i] = (j < half && !interleaved) ? j : (interleaved ? 2 * j : rot_dim + 2 * (j - half));
+        e2[i] = (j < half && !interleaved) ? j + half : e1[i] + 1;
         rc[i] = 1.f; rs[i] = 0.f;
-        if (j < half) sincosf((float)pos * inv_freq[j], &rs[i], &rc[i]);
-        const bool ok = j < n_pairs;
+        if (j < half) {
+            sincosf((float)pos * inv_freq[j], &rs[i], &rc[i]);
+            rs[i] *= amplitude; rc[i] *= amplitude;
+        }
+        const bool ok = j < n_pairs && !w_stride;    // per-column weights are read per head below
         wq1[i] = (ok && q_norm_w) ? q_norm_w[e1[i]] : 1.f; wq2[i] = (ok && q_norm_w) ? q_norm_w[e2[i]] : 1.f;
         wk1[i] = (ok && k_norm_w) ? k_norm_w[e1[i]] : 1.f; wk2[i] = (ok && k_norm_w) ? k_norm_w[e2[i]] : 1.f;
     }
@@ -112,13 +132,16 @@ qk_norm_rope_write_kernel(T* __restrict__ qkv, const float* __restrict__ q_norm_
                 continue;
             }
             const bool normed = is_q ? q_norm_w != nullptr : k_norm_w != nullptr;
-            const float scale = normed ? rsqrtf(ss[u] / (float)hd + eps) : 1.f;
+            const float scale = !normed ? 1.f : row_sumsq ? (is_q ? whole_q : whole_k) : rsqrtf(ss[u] / (float)hd + eps);
             T* dst = (is_k && write_kv) ? k_pages + ((page_base + (head - H)) * page_size + in_page) * hd : nullptr;
+            T* vdst = (is_k && write_kv && v_from_k) ? v_pages + ((page_base + (head - H)) * page_size + in_page) * hd : nullptr;
+            const float* wcol = (normed && w_stride) ? (is_q ? q_norm_w + (size_t)head * hd : k_norm_w + (size_t)(head - H) * hd) : nullptr;
 #pragma unroll
             for (int i = 0; i < PPL; ++i) {
                 if (lane + 32 * i >= n_pairs) break;
-                const float v1 = a[u][i] * scale * (is_q ? wq1[i] : wk1[i]);
-                const float v2 = b[u][i] * scale * (is_q ? wq2[i] : wk2[i]);
+                if (vdst) { vdst[e1[i]] = from_f32<T>(a[u][i]); vdst[e2[i]] = from_f32<T>(b[u][i]); }   // the value is the key as projected
+                const float v1 = a[u][i] * scale * (wcol ? wcol[e1[i]] : is_q ? wq1[i] : wk1[i]);
+                const float v2 = b[u][i] * scale * (wcol ? wcol[e2[i]] : is_q ? wq2[i] : wk2[i]);
                 const float o1 = v1 * rc[i] - v2 * rs[i];          // identity for the unrotated pairs
                 const float o2 = v1 * rs[i] + v2 * rc[i];
                 x[e1[i]] = from_f32<T>(o1);
@@ -127,6 +150,23 @@ qk_norm_rope_write_kernel(T* __restrict__ qkv, const float* __restrict__ q_norm_
             }
         }
     }
+}
+
+// Sums of squares of a token's whole q projection (columns [0, nq)) and whole k projection ([nq, nq + nk)):
+// out[t] = (sum q^2, sum k^2).  One block per token, a fixed order of additions.
+template <typename T>
+__global__ void qk_sumsq_kernel(const T* __restrict__ qkv, long long stride, int nq, int nk, float* __restrict__ out) {
+    __shared__ float scratch[32];
+    const int t = blockIdx.x;
+    pdl_wait();
+    pdl_launch_dependents();
+    const T* row = qkv + (size_t)t * stride;
+    float sq = 0.f, sk = 0.f;
+    for (int i = threadIdx.x; i < nq; i += blockDim.x) { const float v = ld_act(row + i); sq = fmaf(v, v, sq); }
+    for (int i = threadIdx.x; i < nk; i += blockDim.x) { const float v = ld_act(row + nq + i); sk = fmaf(v, v, sk); }
+    sq = block_sum(sq, scratch);
+    sk = block_sum(sk, scratch);
+    if (threadIdx.x == 0) { out[2 * (size_t)t] = sq; out[2 * (size_t)t + 1] = sk; }
 }
 
 constexpr int ATT_WARPS = 4;
@@ -138,7 +178,8 @@ paged_attention_plain_kernel(const T* __restrict__ q, long long q_stride, const 
                              const T* __restrict__ v_pages, const int* __restrict__ block_table,
                              int max_blocks, const int* __restrict__ positions,
                              const int* __restrict__ row_of_token, T* __restrict__ out,
-                             int H, int G, int hd, int page_size, float scale, int window, Bounds bounds) {
+                             int H, int G, int hd, int page_size, float scale, int window, Bounds bounds,
+                             int chunk, int has_sink, float sink, float out_scale) {
     __shared__ float sh_acc[ATT_WARPS][MAX_HD];
     __shared__ float sh_m[ATT_WARPS], sh_l[ATT_WARPS];
     const int t = blockIdx.x, h = blockIdx.y;
@@ -147,7 +188,7 @@ paged_attention_plain_kernel(const T* __restrict__ q, long long q_stride, const 
     const int pos = positions[t];
     const int r = row_of_token[t];
     if (!check_row(bounds, r)) return;               // the same for the whole block
-    const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+    const int lo = first_key(pos, window, chunk);
     const int* bt = block_table + (size_t)r * max_blocks;
 
     float qv[MAX_PER_LANE], acc[MAX_PER_LANE];
@@ -194,7 +235,8 @@ paged_attention_plain_kernel(const T* __restrict__ q, long long q_stride, const 
     float m_all = -INFINITY;
 #pragma unroll
     for (int w = 0; w < ATT_WARPS; ++w) m_all = fmaxf(m_all, sh_m[w]);
-    float l_all = 0.f;
+    if (has_sink) m_all = fmaxf(m_all, sink);           // the sink is one more score, with no value
+    float l_all = has_sink ? expf(sink - m_all) : 0.f;
     float f[ATT_WARPS];
 #pragma unroll
     for (int w = 0; w < ATT_WARPS; ++w) {
@@ -206,7 +248,7 @@ paged_attention_plain_kernel(const T* __restrict__ q, long long q_stride, const 
         float o = 0.f;
 #pragma unroll
         for (int w = 0; w < ATT_WARPS; ++w) o += sh_acc[w][e] * f[w];
-        op[e] = from_f32<T>(o / l_all);
+        op[e] = from_f32<T>(o / l_all * out_scale);
     }
 }
 }  // namespace
@@ -220,18 +262,20 @@ extern "C" int tuff_qk_norm_rope_write(void* qkv, int dtype, const float* q_norm
                                        const int* block_table, int max_blocks, void* k_pages, void* v_pages,
                                        int n_tokens, int H, int G, int hd, int rot_dim, int page_size,
                                        float eps, int write_kv, long long table_rows, long long n_pages, int* status,
+                                       int interleaved, float amplitude, const float* row_sumsq, int v_from_k,
                                        cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (hd < 2 || hd > MAX_HD || (hd & 1) || rot_dim < 0 || rot_dim > hd || (rot_dim & 1) || G < 0 || H < 0) return TUFF_E_SIZE;
     if (write_kv && page_size < 1) return TUFF_E_SIZE;
     // few tokens: spread a token's heads over several blocks so that the launch fills more SMs
-    const int n_heads = H + 2 * G;
+    const int n_heads = H + (v_from_k ? G : 2 * G);
     int per_token = n_tokens >= 512 ? 1 : ceil_div(n_heads, QKV_WARPS);
     if (per_token > 65535) per_token = 65535;
     dim3 grid(n_tokens, per_token);
 #define QK_GO(T, PPL) return launch_pdl(qk_norm_rope_write_kernel<T, PPL>, grid, dim3(QKV_WARPS * 32), 0, stream, \
         (T*)qkv, q_norm_w, k_norm_w, inv_freq, positions, row_of_token, block_table, max_blocks, \
-        (T*)k_pages, (T*)v_pages, H, G, hd, rot_dim, page_size, eps, write_kv, Bounds{table_rows, n_pages, status})
+        (T*)k_pages, (T*)v_pages, H, G, hd, rot_dim, page_size, eps, write_kv, Bounds{table_rows, n_pages, status}, \
+        interleaved, amplitude, row_sumsq, v_from_k)
     if (dtype == TUFF_F32) {
         if (hd <= 64) QK_GO(float, 1); else if (hd <= 128) QK_GO(float, 2); else QK_GO(float, 4);
     } else if (dtype == TUFF_BF16) {
@@ -241,24 +285,37 @@ extern "C" int tuff_qk_norm_rope_write(void* qkv, int dtype, const float* q_norm
     return TUFF_E_DTYPE;
 }
 
+// out[t] = (sum of squares of qkv[t, 0:nq], of qkv[t, nq:nq+nk]), for a norm over whole projections.
+extern "C" int tuff_qk_sumsq(const void* qkv, int dtype, long long stride, int nq, int nk, float* out, int n_tokens,
+                             cudaStream_t stream) {
+    if (n_tokens <= 0) return 0;
+    if (dtype == TUFF_F32) return launch_pdl(qk_sumsq_kernel<float>, dim3(n_tokens), dim3(256), 0, stream, (const float*)qkv, stride, nq, nk, out);
+    if (dtype == TUFF_BF16) return launch_pdl(qk_sumsq_kernel<bf16>, dim3(n_tokens), dim3(256), 0, stream, (const bf16*)qkv, stride, nq, nk, out);
+    return TUFF_E_DTYPE;
+}
+
 // q: [n_tokens, H, hd] with a row stride of q_stride elements; out: [n_tokens, H*hd].
+// chunk > 0: a query sees only keys of its own chunk of `chunk` positions; has_sink: exp(sink) joins the
+// softmax's denominator; the result is multiplied by out_scale.
 extern "C" int tuff_paged_attention_plain(const void* q, long long q_stride, const void* k_pages,
                                           const void* v_pages, int dtype, const int* block_table, int max_blocks,
                                           const int* positions, const int* row_of_token, void* out,
                                           int n_tokens, int H, int G, int hd, int page_size, float scale,
                                           int window, long long table_rows, long long n_pages, int* status,
-                                          cudaStream_t stream) {
+                                          int chunk, int has_sink, float sink, float out_scale, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (hd < 1 || hd > MAX_HD || G < 1 || H % G != 0 || page_size < 1 || H > 65535) return TUFF_E_SIZE;
     dim3 grid(n_tokens, H);
     if (dtype == TUFF_F32)
         paged_attention_plain_kernel<float><<<grid, ATT_WARPS * 32, 0, stream>>>(
             (const float*)q, q_stride, (const float*)k_pages, (const float*)v_pages, block_table, max_blocks,
-            positions, row_of_token, (float*)out, H, G, hd, page_size, scale, window, Bounds{table_rows, n_pages, status});
+            positions, row_of_token, (float*)out, H, G, hd, page_size, scale, window, Bounds{table_rows, n_pages, status},
+            chunk, has_sink, sink, out_scale);
     else if (dtype == TUFF_BF16)
         paged_attention_plain_kernel<bf16><<<grid, ATT_WARPS * 32, 0, stream>>>(
             (const bf16*)q, q_stride, (const bf16*)k_pages, (const bf16*)v_pages, block_table, max_blocks,
-            positions, row_of_token, (bf16*)out, H, G, hd, page_size, scale, window, Bounds{table_rows, n_pages, status});
+            positions, row_of_token, (bf16*)out, H, G, hd, page_size, scale, window, Bounds{table_rows, n_pages, status},
+            chunk, has_sink, sink, out_scale);
     else
         return TUFF_E_DTYPE;
     return launch_status();

@@ -11,9 +11,11 @@
 #include <algorithm>
 
 // ---------------------------------------------------------------- embedding
+// `pos_table` (may be null): a learned vector per position, added unscaled: x = E[token] + P[position].
 template <typename WT>
 __global__ void embed_kernel(const int* __restrict__ tokens, const WT* __restrict__ table,
-                             float* __restrict__ out, int d, int vocab) {
+                             float* __restrict__ out, int d, int vocab, const int* __restrict__ positions,
+                             const WT* __restrict__ pos_table, int n_positions) {
     const int t = blockIdx.x;
     pdl_launch_dependents();
     pdl_wait();
@@ -21,18 +23,30 @@ __global__ void embed_kernel(const int* __restrict__ tokens, const WT* __restric
     const bool ok = tok >= 0 && tok < vocab;
     if (!ok) tok = 0;
     const WT* row = table + (size_t)tok * d;
+    const WT* prow = nullptr;
+    if (pos_table) {
+        const int p = ld_act(positions + t);
+        if (p >= 0 && p < n_positions) prow = pos_table + (size_t)p * d;
+    }
     float* o = out + (size_t)t * d;
-    for (int i = threadIdx.x; i < d; i += blockDim.x) o[i] = ok ? to_f32(row[i]) : 0.f;
+    for (int i = threadIdx.x; i < d; i += blockDim.x) {
+        float v = ok ? to_f32(row[i]) : 0.f;
+        if (prow) v += to_f32(prow[i]);
+        o[i] = v;
+    }
 }
 
 extern "C" int tuff_embed(const int* tokens, const void* table, int table_dtype, float* out,
-                          int n_tokens, int d, int vocab, cudaStream_t stream) {
+                          int n_tokens, int d, int vocab, const int* positions, const void* pos_table,
+                          int n_positions, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     const int threads = d >= 1024 ? 256 : 128;
     if (table_dtype == TUFF_F32)
-        return launch_pdl(embed_kernel<float>, dim3(n_tokens), dim3(threads), 0, stream, tokens, (const float*)table, out, d, vocab);
+        return launch_pdl(embed_kernel<float>, dim3(n_tokens), dim3(threads), 0, stream, tokens, (const float*)table, out, d, vocab,
+                          positions, (const float*)pos_table, n_positions);
     else if (table_dtype == TUFF_BF16)
-        return launch_pdl(embed_kernel<bf16>, dim3(n_tokens), dim3(threads), 0, stream, tokens, (const bf16*)table, out, d, vocab);
+        return launch_pdl(embed_kernel<bf16>, dim3(n_tokens), dim3(threads), 0, stream, tokens, (const bf16*)table, out, d, vocab,
+                          positions, (const bf16*)pos_table, n_positions);
     return TUFF_E_DTYPE;
 }
 
@@ -137,6 +151,124 @@ extern "C" int tuff_rmsnorm(const void* x, int x_dtype, const float* w, void* ou
     else return TUFF_E_DTYPE;
 #undef LAUNCH
     return rc ? rc : launch_status();
+}
+
+// ------------------------------------------------- norm after the sum (post-norm layers)
+// A layer that norms after the addition, x <- norm(alpha * x + f(x)), keeps three views of the stream:
+//   x  the normed stream itself (fp32),
+//   h  the same in the activation dtype, which the next sublayer's products read,
+//   s  alpha * x (fp32), into which the next sublayer's last product adds.
+// `rmsnorm_fork` reads the finished sum s_in and writes all three (any of them may be null; s_out may
+// be s_in itself: a thread re-reads an element just before it overwrites it).  One block per row, the
+// squares added in the same order as in rmsnorm_kernel, so a row does not depend on the batch.
+template <typename HT>
+__global__ void rmsnorm_fork_kernel(const float* s_in, const float* __restrict__ w, float eps, float alpha,
+                                    float* __restrict__ x_out, HT* __restrict__ h_out, float* s_out, int d) {
+    __shared__ float scratch[32];
+    const int r = blockIdx.x;
+    pdl_wait();
+    const float* sr = s_in + (size_t)r * d;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < d; i += blockDim.x) {
+        const float v = ld_act(sr + i);
+        ss = fmaf(v, v, ss);
+    }
+    ss = block_sum(ss, scratch);
+    pdl_launch_dependents();
+    const float scale = rsqrtf(ss / (float)d + eps);
+    for (int i = threadIdx.x; i < d; i += blockDim.x) {
+        const float v = ld_act(sr + i) * scale * w[i];
+        if (x_out) x_out[(size_t)r * d + i] = v;
+        if (h_out) h_out[(size_t)r * d + i] = from_f32<HT>(v);
+        if (s_out) s_out[(size_t)r * d + i] = alpha * v;
+    }
+}
+
+// Warp-per-row variant for many rows (bf16 path only, like rmsnorm_rows_kernel).
+__global__ void __launch_bounds__(256)
+rmsnorm_fork_rows_kernel(const float* s_in, const float* __restrict__ w, float eps, float alpha,
+                         float* __restrict__ x_out, bf16* __restrict__ h_out, float* s_out, int n_rows, int d) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int r = blockIdx.x * (blockDim.x >> 5) + warp;
+    pdl_wait();
+    pdl_launch_dependents();
+    if (r >= n_rows) return;
+    const float* sr = s_in + (size_t)r * d;
+    float4 v[RMS_VEC];
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < RMS_VEC; ++i) {
+        const int k = (i * 32 + lane) * 4;
+        if (k < d) v[i] = __ldcg(reinterpret_cast<const float4*>(sr + k));
+    }
+#pragma unroll
+    for (int i = 0; i < RMS_VEC; ++i) {
+        const int k = (i * 32 + lane) * 4;
+        if (k < d) {
+            ss = fmaf(v[i].x, v[i].x, ss); ss = fmaf(v[i].y, v[i].y, ss);
+            ss = fmaf(v[i].z, v[i].z, ss); ss = fmaf(v[i].w, v[i].w, ss);
+        }
+    }
+    ss = warp_sum(ss);
+    const float scale = rsqrtf(ss / (float)d + eps);
+#pragma unroll
+    for (int i = 0; i < RMS_VEC; ++i) {
+        const int k = (i * 32 + lane) * 4;
+        if (k < d) {
+            const float4 g = *reinterpret_cast<const float4*>(w + k);
+            const float a = v[i].x * scale * g.x, b = v[i].y * scale * g.y, c = v[i].z * scale * g.z, e = v[i].w * scale * g.w;
+            const size_t o = (size_t)r * d + k;
+            if (x_out) *reinterpret_cast<float4*>(x_out + o) = make_float4(a, b, c, e);
+            if (s_out) *reinterpret_cast<float4*>(s_out + o) = make_float4(alpha * a, alpha * b, alpha * c, alpha * e);
+            if (h_out) {
+                __nv_bfloat162 lo = __floats2bfloat162_rn(a, b), hi = __floats2bfloat162_rn(c, e);
+                *reinterpret_cast<uint2*>(h_out + o) = make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
+            }
+        }
+    }
+}
+
+extern "C" int tuff_rmsnorm_fork(const float* s_in, const float* w, float eps, float alpha, float* x_out, void* h_out,
+                                 int h_dtype, float* s_out, int n_rows, int d, cudaStream_t stream) {
+    if (n_rows <= 0) return 0;
+    auto al16 = [](const void* p) { return !((uintptr_t)p & 15); };
+    if (h_dtype == TUFF_BF16 && n_rows > 16 && d % 4 == 0 && d <= 128 * RMS_VEC && al16(s_in) && al16(w) && al16(x_out) &&
+        al16(s_out) && !((uintptr_t)h_out & 7)) {
+        const int warps = n_rows >= 2048 ? 8 : n_rows >= 512 ? 4 : n_rows >= 128 ? 2 : 1;
+        return launch_pdl(rmsnorm_fork_rows_kernel, dim3(ceil_div(n_rows, warps)), dim3(32 * warps), 0, stream, s_in, w, eps, alpha,
+                          x_out, (bf16*)h_out, s_out, n_rows, d);
+    }
+    if (h_dtype == TUFF_BF16)
+        return launch_pdl(rmsnorm_fork_kernel<bf16>, dim3(n_rows), dim3(256), 0, stream, s_in, w, eps, alpha, x_out, (bf16*)h_out, s_out, d);
+    if (h_dtype == TUFF_F32)
+        return launch_pdl(rmsnorm_fork_kernel<float>, dim3(n_rows), dim3(256), 0, stream, s_in, w, eps, alpha, x_out, (float*)h_out, s_out, d);
+    return TUFF_E_DTYPE;
+}
+
+// The same three views from a stream that is already normed (the first layer, after the embedding):
+// h = x in the activation dtype, s = alpha * x.
+template <typename HT>
+__global__ void stream_fork_kernel(const float* __restrict__ x, float alpha, HT* __restrict__ h_out,
+                                   float* __restrict__ s_out, size_t n) {
+    pdl_wait();
+    pdl_launch_dependents();
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+        const float v = ld_act(x + i);
+        if (h_out) h_out[i] = from_f32<HT>(v);
+        s_out[i] = alpha * v;
+    }
+}
+
+extern "C" int tuff_stream_fork(const float* x, float alpha, void* h_out, int h_dtype, float* s_out, long long n,
+                                cudaStream_t stream) {
+    if (n <= 0) return 0;
+    const int threads = 256;
+    const int blocks = (int)std::min((n + threads - 1) / threads, (long long)sm_count() * 16);
+    if (h_dtype == TUFF_BF16)
+        return launch_pdl(stream_fork_kernel<bf16>, dim3(blocks), dim3(threads), 0, stream, x, alpha, (bf16*)h_out, s_out, (size_t)n);
+    if (h_dtype == TUFF_F32)
+        return launch_pdl(stream_fork_kernel<float>, dim3(blocks), dim3(threads), 0, stream, x, alpha, (float*)h_out, s_out, (size_t)n);
+    return TUFF_E_DTYPE;
 }
 
 // ------------------------------------------------------------------- SwiGLU

@@ -44,6 +44,14 @@ TUFF_HD size_t page_elem(long long page, int kv_head, int offset, int kv_heads, 
 // First element of a slot's state of `per_slot` elements.
 TUFF_HD size_t slot_elem(long long slot, size_t per_slot) { return (size_t)slot * per_slot; }
 
+// The oldest key a query at `pos` sees: all keys from 0, or only the latest `window` (window > 0), or only
+// those of its own chunk of `chunk` positions, counted from position 0 (chunk > 0); the later of the two bounds.
+TUFF_HD int first_key(int pos, int window, int chunk) {
+    int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+    if (chunk > 0) { const int c = pos / chunk * chunk; if (c > lo) lo = c; }
+    return lo;
+}
+
 // What a kernel needs for the checks: the sizes of the pool it indexes and where to leave a code.
 // n_rows: rows of the block table (or of the slot table); n: pages in the pool, or state slots.
 struct Bounds {

@@ -89,7 +89,7 @@ class ModelRunner:
         """Fills every page and state with small random numbers (see `synthetic_fill`)."""
         g = torch.Generator(device=self.device)
         g.manual_seed(seed)
-        for st in self.cache.storages:
+        for st in self.cache.leaf_storages():
             for name in ("k_pages", "v_pages", "state"):
                 t = getattr(st, name, None)
                 if t is not None:

@@ -75,16 +75,24 @@ def _i32(t: torch.Tensor | None, name: str) -> None:
 
 
 # ----------------------------------------------------------------- elementwise
-def embed(tokens: torch.Tensor, table: torch.Tensor, out: torch.Tensor) -> None:
-    """out[t, :] = table[tokens[t], :] as float32."""
+def embed(tokens: torch.Tensor, table: torch.Tensor, out: torch.Tensor, positions: torch.Tensor | None = None,
+          pos_table: torch.Tensor | None = None) -> None:
+    """out[t, :] = table[tokens[t], :] as float32, plus pos_table[positions[t], :] if a table of learned
+    position vectors is given."""
     _written(out)
     _i32(tokens, "tokens")
     n, d = out.shape
     assert out.dtype == torch.float32 and table.shape[1] == d and tokens.numel() == n
     _contig(table, "table"); _contig(out, "out")
+    n_pos = 0
+    if pos_table is not None:
+        assert positions is not None and pos_table.dtype == table.dtype and pos_table.shape[1] == d
+        _i32(positions, "positions"); _contig(pos_table, "pos_table")
+        n_pos = pos_table.shape[0]
     lib = load_library("elementwise")
     _check(lib.tuff_embed(_ptr(tokens), _ptr(table), dtype_code(table), _ptr(out), c_int(n), c_int(d),
-                          c_int(table.shape[0]), _stream()), "embed")
+                          c_int(table.shape[0]), _ptr(positions if pos_table is not None else None), _ptr(pos_table),
+                          c_int(n_pos), _stream()), "embed")
 
 
 def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor,
@@ -98,6 +106,36 @@ def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor
     lib = load_library("elementwise")
     _check(lib.tuff_rmsnorm(_ptr(x), dtype_code(x), _ptr(weight), _ptr(out), dtype_code(out), _ptr(row_index),
                             c_int(n), c_int(d), c_float(eps), _stream()), "rmsnorm")
+
+
+def rmsnorm_fork(s: torch.Tensor, weight: torch.Tensor, eps: float, alpha: float, x_out: torch.Tensor | None,
+                 h_out: torch.Tensor | None, s_out: torch.Tensor | None, h_dtype: torch.dtype) -> None:
+    """The norm of a layer that norms after the sum, with the three views of the stream it feeds:
+    x_out = rmsnorm(s) * weight (fp32), h_out = the same in the activation dtype, s_out = alpha * x_out
+    (fp32; may be `s` itself).  Any of the three may be None."""
+    n, d = s.shape
+    assert s.dtype == torch.float32 and weight.dtype == torch.float32 and weight.numel() == d
+    _contig(s, "s")
+    for t, dt in ((x_out, torch.float32), (h_out, h_dtype), (s_out, torch.float32)):
+        if t is not None:
+            assert t.shape == (n, d) and t.dtype == dt
+            _contig(t, "out"); _written(t)
+    lib = load_library("elementwise")
+    _check(lib.tuff_rmsnorm_fork(_ptr(s), _ptr(weight), c_float(eps), c_float(alpha), _ptr(x_out), _ptr(h_out),
+                                 c_int(F32 if h_dtype == torch.float32 else BF16), _ptr(s_out), c_int(n), c_int(d),
+                                 _stream()), "rmsnorm_fork")
+
+
+def stream_fork(x: torch.Tensor, alpha: float, h_out: torch.Tensor | None, s_out: torch.Tensor) -> None:
+    """h_out = x in the activation dtype (None: not wanted), s_out = alpha * x."""
+    assert x.dtype == torch.float32 and s_out.dtype == torch.float32 and s_out.shape == x.shape
+    _contig(x, "x"); _contig(s_out, "s_out"); _written(s_out)
+    if h_out is not None:
+        assert h_out.shape == x.shape
+        _contig(h_out, "h_out"); _written(h_out)
+    lib = load_library("elementwise")
+    _check(lib.tuff_stream_fork(_ptr(x), c_float(alpha), _ptr(h_out), c_int(dtype_code(h_out) if h_out is not None else F32),
+                                _ptr(s_out), c_longlong(x.numel()), _stream()), "stream_fork")
 
 
 def swiglu(gate_up: torch.Tensor, out: torch.Tensor, block: int = 0) -> None:
@@ -521,13 +559,18 @@ def qk_norm_rope_write(qkv: torch.Tensor, q_norm_w: torch.Tensor | None, k_norm_
                        inv_freq: torch.Tensor | None, positions: torch.Tensor, row_of_token: torch.Tensor,
                        block_table: torch.Tensor | None, k_pages: torch.Tensor | None,
                        v_pages: torch.Tensor | None, H: int, G: int, hd: int, rot_dim: int, eps: float,
-                       write_kv: bool = True) -> None:
-    """Per-head RMSNorm + NeoX rotation of q and k in place; K and V stored in their pages.
+                       write_kv: bool = True, interleaved: bool = False, amplitude: float = 1.0,
+                       whole_norm: bool = False, v_from_k: bool = False) -> None:
+    """RMSNorm + rotation of q and k in place; K and V stored in their pages.
 
     k_pages / v_pages: [num_pages, G, page_size, hd]; block_table: [rows, max_blocks] int32.
+    The norm is per head with a weight [hd], or (`whole_norm`) over a token's whole q projection and whole
+    k projection with weights [H*hd] and [G*hd].  The rotation pairs element i with i + rot_dim/2, or
+    (`interleaved`) element 2i with 2i+1; cos and sin are multiplied by `amplitude`.  `v_from_k`: qkv holds
+    no value heads and the value pages receive the keys as projected (before norm and rotation).
     """
     n = qkv.shape[0]
-    assert qkv.shape[1] == (H + 2 * G) * hd
+    assert qkv.shape[1] == (H + (G if v_from_k else 2 * G)) * hd
     _contig(qkv, "qkv"); _i32(positions, "positions"); _i32(row_of_token, "row_of_token")
     page_size, max_blocks = 1, 0
     if write_kv:
@@ -539,22 +582,32 @@ def qk_norm_rope_write(qkv: torch.Tensor, q_norm_w: torch.Tensor | None, k_norm_
         page_size, max_blocks = k_pages.shape[2], block_table.shape[1]
     if rot_dim:
         assert inv_freq is not None and inv_freq.dtype == torch.float32 and inv_freq.numel() == rot_dim // 2
-    for wv in (q_norm_w, k_norm_w):
-        assert wv is None or (wv.dtype == torch.float32 and wv.numel() == hd)
+    for wv, heads in ((q_norm_w, H), (k_norm_w, G)):
+        assert wv is None or (wv.dtype == torch.float32 and wv.numel() == (heads * hd if whole_norm else hd))
     lib = load_library("attention_plain")
+    sumsq = None
+    if whole_norm:
+        assert q_norm_w is not None and k_norm_w is not None
+        sumsq = torch.empty((n, 2), dtype=torch.float32, device=qkv.device)
+        _check(lib.tuff_qk_sumsq(_ptr(qkv), dtype_code(qkv), c_longlong(qkv.stride(0)), c_int(H * hd), c_int(G * hd),
+                                 _ptr(sumsq), c_int(n), _stream()), "qk_sumsq")
     _check(lib.tuff_qk_norm_rope_write(_ptr(qkv), dtype_code(qkv), _ptr(q_norm_w), _ptr(k_norm_w), _ptr(inv_freq),
                                        _ptr(positions), _ptr(row_of_token), _ptr(block_table), c_int(max_blocks),
                                        _ptr(k_pages), _ptr(v_pages), c_int(n), c_int(H), c_int(G), c_int(hd),
                                        c_int(rot_dim), c_int(page_size), c_float(eps), c_int(1 if write_kv else 0),
                                        c_longlong(block_table.shape[0] if write_kv else 0),
                                        c_longlong(k_pages.shape[0] if write_kv else 0), _ptr(status_word(qkv.device)),
-                                       _stream()), "qk_norm_rope_write")
+                                       c_int(1 if interleaved else 0), c_float(amplitude), _ptr(sumsq),
+                                       c_int(1 if v_from_k else 0), _stream()), "qk_norm_rope_write")
 
 
 def paged_attention_plain(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, block_table: torch.Tensor,
                           positions: torch.Tensor, row_of_token: torch.Tensor, out: torch.Tensor, H: int, G: int,
-                          hd: int, scale: float, window: int = 0) -> None:
-    """Causal attention of each token over its request's cached keys (the last `window` if > 0).
+                          hd: int, scale: float, window: int = 0, chunk: int = 0, sink: float | None = None,
+                          out_scale: float = 1.0) -> None:
+    """Causal attention of each token over its request's cached keys (the last `window` if > 0; only
+    those of its own chunk of `chunk` positions if > 0).  `sink`: a further score without a value in the
+    softmax's denominator.  The result is multiplied by `out_scale`.
 
     q: [n, >= H*hd] (row stride taken from the tensor), out: [n, H*hd].
     """
@@ -568,7 +621,9 @@ def paged_attention_plain(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch
                                           _ptr(positions), _ptr(row_of_token), _ptr(out), c_int(n), c_int(H),
                                           c_int(G), c_int(hd), c_int(k_pages.shape[2]), c_float(scale),
                                           c_int(window), c_longlong(block_table.shape[0]), c_longlong(k_pages.shape[0]),
-                                          _ptr(status_word(q.device)), _stream()), "paged_attention_plain")
+                                          _ptr(status_word(q.device)), c_int(chunk or 0), c_int(0 if sink is None else 1),
+                                          c_float(0.0 if sink is None else sink), c_float(out_scale), _stream()),
+           "paged_attention_plain")
 
 
 _attn_state: dict = {}
@@ -677,7 +732,8 @@ def attention_prefill_tc(q, k_pages, v_pages, block_table, positions, cu_q, out,
 
 def paged_attention(q, k_pages, v_pages, block_table, positions, row_of_token, out, H, G, hd, scale,
                     window: int = 0, ctx=None, cu_q=None, all_single: bool | None = None,
-                    max_seq_len: int | None = None, single_prefix: int | None = None) -> None:
+                    max_seq_len: int | None = None, single_prefix: int | None = None, chunk: int = 0,
+                    sink: float | None = None, out_scale: float = 1.0) -> None:
     """Attention over the paged cache by the kernel that suits the batch: the tensor-core kernels
     for bf16 with head size 64 or 128 (the sliced one for rows that bring a single token, the
     blocked ones for portions of prompts), the plain kernel for everything else.  `single_prefix`:
@@ -689,6 +745,10 @@ def paged_attention(q, k_pages, v_pages, block_table, positions, row_of_token, o
         max_seq_len = ctx.max_seq_len if max_seq_len is None else max_seq_len
         single_prefix = ctx.single_prefix if single_prefix is None else single_prefix
     assert q.stride(1) == 1 and out.shape == (q.shape[0], H * hd) and q.dtype == k_pages.dtype == out.dtype
+    if chunk or sink is not None or out_scale != 1.0:
+        paged_attention_plain(q, k_pages, v_pages, block_table, positions, row_of_token, out, H, G, hd, scale, window,
+                              chunk=chunk, sink=sink, out_scale=out_scale)
+        return
     n_rows = 0 if cu_q is None else cu_q.numel() - 1
     sp = int(single_prefix or 0)
     if (not all_single and cu_q is not None and 0 < sp < n_rows and attention_flash_supported(q, k_pages, H, G, hd)):
@@ -731,6 +791,60 @@ def _attention_portions(q, k_pages, v_pages, block_table, positions, row_of_toke
         _i32(row_of_token, "row_of_token")
         attention_prefill(q, k_pages, v_pages, block_table, positions, row_of_token, cu_q, out, H, G, hd, scale,
                           window, n_tokens=n_tokens)
+
+
+# ------------------------------------------------------------ linear attention
+def linear_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, state: torch.Tensor, slot_of_row: torch.Tensor,
+                     cu_q: torch.Tensor, out: torch.Tensor, H: int, dk: int, dv: int, head_decay: torch.Tensor | None = None,
+                     gate: torch.Tensor | None = None, gate_bias: torch.Tensor | None = None, tau: float = 1.0,
+                     q_scale: float = 1.0, silu: bool = False) -> None:
+    """Per request and head S_t = diag(a_t) S_(t-1) + k_t v_t^T, o_t = S_t^T q_t, over a batch of portions;
+    the state [slots, H, dk, dv] (fp32) of each row's slot is continued and left updated.
+    q, k [n, >= H*dk] and v [n, >= H*dv] are views with a row stride; out fp32 [n, H*dv].
+    Decay: `head_decay` fp32 [H] (one factor per head), or `gate` fp32 [n, H*dk] (+ `gate_bias` [H*dk]) with
+    a = sigmoid(gate + bias)^(1/tau) per key channel and token.  `silu`: applied to q, k and v; q * q_scale."""
+    _written(out)
+    n = out.shape[0]
+    assert (head_decay is None) != (gate is None)
+    assert q.dtype == k.dtype == v.dtype and out.dtype == torch.float32 and state.dtype == torch.float32
+    assert q.shape[0] == k.shape[0] == v.shape[0] == n and out.shape == (n, H * dv) and state.shape[1:] == (H, dk, dv)
+    for t in (q, k, v, out):
+        assert t.stride(1) == 1
+    _contig(state, "state"); _i32(slot_of_row, "slot_of_row"); _i32(cu_q, "cu_q")
+    if head_decay is not None:
+        assert head_decay.dtype == torch.float32 and head_decay.numel() == H
+    else:
+        assert gate.dtype == torch.float32 and gate.shape == (n, H * dk) and gate.stride(1) == 1
+        assert gate_bias is None or (gate_bias.dtype == torch.float32 and gate_bias.numel() == H * dk)
+    lib = load_library("linear_attention")
+    _check(lib.tuff_linear_attention(_ptr(q), c_longlong(q.stride(0)), _ptr(k), c_longlong(k.stride(0)), _ptr(v),
+                                     c_longlong(v.stride(0)), dtype_code(q), c_int(0 if gate is None else 1),
+                                     _ptr(head_decay), _ptr(gate), c_longlong(gate.stride(0) if gate is not None else 0),
+                                     _ptr(gate_bias), c_float(1.0 / tau), c_float(q_scale), c_int(1 if silu else 0),
+                                     _ptr(state), c_longlong(state.shape[0]), _ptr(slot_of_row), _ptr(cu_q), _ptr(out),
+                                     c_longlong(out.stride(0)), c_int(cu_q.numel() - 1), c_int(H), c_int(dk), c_int(dv),
+                                     _ptr(status_word(out.device)), _stream()), "linear_attention")
+
+
+GATE_NONE, GATE_SIGMOID, GATE_SILU = 0, 1, 2
+
+
+def gated_group_norm(o: torch.Tensor, gate: torch.Tensor | None, weight: torch.Tensor, eps: float, group: int,
+                     out: torch.Tensor, gate_act: int = GATE_NONE, out_scale: float = 1.0) -> None:
+    """out = rmsnorm over groups of `group` columns of o (fp32) * weight[column % len(weight)] * act(gate) * out_scale;
+    gate [n, >= width] is a view in out's dtype with a row stride (ignored for GATE_NONE)."""
+    _written(out)
+    n, width = o.shape
+    assert o.dtype == torch.float32 and weight.dtype == torch.float32 and out.shape == (n, width)
+    assert width % group == 0 and weight.numel() in (group, width)
+    _contig(o, "o"); _contig(out, "out")
+    if gate_act != GATE_NONE:
+        assert gate is not None and gate.dtype == out.dtype and gate.shape[0] == n and gate.shape[1] >= width and gate.stride(1) == 1
+    lib = load_library("linear_attention")
+    _check(lib.tuff_gated_group_norm(_ptr(o), _ptr(gate), c_longlong(gate.stride(0) if gate is not None else 0),
+                                     dtype_code(out), _ptr(weight), c_int(weight.numel()), c_float(eps), c_int(gate_act),
+                                     c_float(out_scale), _ptr(out), c_int(n), c_int(width), c_int(group), _stream()),
+           "gated_group_norm")
 
 
 # -------------------------------------------------------------------- sampling

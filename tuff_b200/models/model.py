@@ -16,9 +16,9 @@ from .spec import ModelSpec, ScheduleEntry
 class BuiltLayer:
     block: Part
     mixer: Part
-    ffn: Part
+    ffn: Part | None
     mixer_norm: Part
-    ffn_norm: Part
+    ffn_norm: Part | None
 
 
 class Model:
@@ -31,11 +31,13 @@ class Model:
         self._bound: List[Tuple[Part, PartSpec]] = [(self.embedding, spec.embedding),
                                                     (self.final_norm, spec.final_norm), (self.head, spec.head)]
         for ls in spec.layers:
-            bl = BuiltLayer(BLOCKS.build(ls.block), MIXERS.build(ls.mixer), FEED_FORWARDS.build(ls.ffn),
-                            NORMS.build(ls.mixer_norm), NORMS.build(ls.ffn_norm))
+            bl = BuiltLayer(BLOCKS.build(ls.block), MIXERS.build(ls.mixer),
+                            FEED_FORWARDS.build(ls.ffn) if ls.ffn is not None else None,
+                            NORMS.build(ls.mixer_norm), NORMS.build(ls.ffn_norm) if ls.ffn_norm is not None else None)
             self.layers.append(bl)
-            self._bound += [(bl.block, ls.block), (bl.mixer, ls.mixer), (bl.ffn, ls.ffn),
-                            (bl.mixer_norm, ls.mixer_norm), (bl.ffn_norm, ls.ffn_norm)]
+            self._bound += [(part, ps) for part, ps in ((bl.block, ls.block), (bl.mixer, ls.mixer), (bl.ffn, ls.ffn),
+                                                         (bl.mixer_norm, ls.mixer_norm), (bl.ffn_norm, ls.ffn_norm))
+                            if part is not None]
         self.schedule: List[ScheduleEntry] = spec.resolved_schedule()
         # blocks written before `next_norm` existed (or that have no use for it) are called without it
         self._takes_next_norm = ["next_norm" in inspect.signature(bl.block.forward).parameters for bl in self.layers]

@@ -18,9 +18,9 @@ from ..parts.base import PartSpec
 @dataclass
 class LayerSpec:
     mixer: PartSpec
-    ffn: PartSpec
+    ffn: PartSpec | None              # None: the layer has no feed-forward (and no second norm)
     mixer_norm: PartSpec
-    ffn_norm: PartSpec
+    ffn_norm: PartSpec | None
     block: PartSpec = field(default_factory=lambda: PartSpec("prenorm"))
 
 

@@ -8,6 +8,15 @@ q, k and v projections are stacked into one [(H+2G)*hd, d] matrix when bound.
 Optional, all parameters: the q/k norm (`qk_norm_eps=None` switches it off), the
 position encoding (a PartSpec or None), a window of keys, the score scale.
 A layer that runs on another layer's cache (`reads_only`) projects q alone.
+
+Further options, for other designs: `qk_norm_span="projection"` norms a token's whole q
+projection (and whole k projection) at once, with weights of that size, instead of
+head by head; `values="keys"` has no v projection: the values are the keys as
+projected, before norm and rotation; `chunk=C` lets a query see only the keys of its
+own chunk of C positions (counted from position 0 of the sequence); `sink=s` adds a
+score s without a value to every softmax (s = 0: one is added to the denominator);
+`out_scale` multiplies the attention output before it is rounded for the output
+projection (a branch's weight in a sum of mixers).
 """
 from __future__ import annotations
 
@@ -25,8 +34,17 @@ class GQAAttention(Mixer):
 
     def __init__(self, d_model: int, num_heads: int, num_kv_heads: int, head_dim: int,
                  qk_norm_eps: float | None = None, position_encoding: PartSpec | dict | None = None,
-                 window: int | None = None, scale: float | None = None):
+                 window: int | None = None, scale: float | None = None, qk_norm_span: str = "head",
+                 values: str = "projection", chunk: int | None = None, sink: float | None = None,
+                 out_scale: float = 1.0):
         self.d, self.H, self.G, self.hd = int(d_model), int(num_heads), int(num_kv_heads), int(head_dim)
+        if qk_norm_span not in ("head", "projection") or values not in ("projection", "keys"):
+            raise ValueError(f"gqa_attention: qk_norm_span {qk_norm_span!r} / values {values!r} are not known")
+        self.whole_norm = qk_norm_span == "projection"
+        self.v_from_k = values == "keys"
+        self.chunk = None if not chunk else int(chunk)
+        self.sink = None if sink is None else float(sink)
+        self.out_scale = float(out_scale)
         if self.H % self.G:
             raise ValueError(f"num_heads {self.H} is not a multiple of num_kv_heads {self.G}")
         self.qk_norm_eps = None if qk_norm_eps is None else float(qk_norm_eps)
@@ -40,9 +58,13 @@ class GQAAttention(Mixer):
         H, G, hd, d = self.H, self.G, self.hd, self.d
         decls = {"q_proj": WeightDecl((H * hd, d)), "k_proj": WeightDecl((G * hd, d)),
                  "v_proj": WeightDecl((G * hd, d)), "out_proj": WeightDecl((d, H * hd))}
+        if self.v_from_k:
+            del decls["v_proj"]
         if self.qk_norm_eps is not None:
-            decls["q_layernorm"] = WeightDecl((hd,), role="vector", init="norm")
-            decls["k_layernorm"] = WeightDecl((hd,), role="vector", init="norm")
+            decls["q_layernorm"] = WeightDecl((H * hd if self.whole_norm else hd,), role="vector", init="norm")
+            decls["k_layernorm"] = WeightDecl((G * hd if self.whole_norm else hd,), role="vector", init="norm")
+        elif self.whole_norm:
+            raise ValueError("gqa_attention: qk_norm_span='projection' needs qk_norm_eps")
         return decls
 
     def reserve(self, device, max_rows, max_context):
@@ -50,11 +72,12 @@ class GQAAttention(Mixer):
             ops.reserve_attention_workspace(device, max_rows, max_context, self.H, self.G, self.hd)
 
     def cache_need(self):
-        return PagedKVNeed(kv_heads=self.G, head_dim=self.hd, window=self.window)
+        return PagedKVNeed(kv_heads=self.G, head_dim=self.hd, window=self.window, chunk=self.chunk)
 
     def bind(self, weights, act_dtype):
         super().bind(weights, act_dtype)
-        self.wqkv = torch.cat([weights["q_proj"], weights["k_proj"], weights["v_proj"]], dim=0).contiguous()
+        self.wqkv = torch.cat([weights["q_proj"], weights["k_proj"]] +
+                              ([] if self.v_from_k else [weights["v_proj"]]), dim=0).contiguous()
         self.wq = self.wqkv[: self.H * self.hd]
         self.wo = weights["out_proj"]
         self.qn = weights.get("q_layernorm")
@@ -65,8 +88,11 @@ class GQAAttention(Mixer):
         T = h.shape[0]
         H, G, hd = self.H, self.G, self.hd
         g_here = 0 if reads_only else G
-        qkv = torch.empty((T, (H + 2 * g_here) * hd), dtype=self.act_dtype, device=h.device)
+        if reads_only and self.whole_norm:
+            raise ValueError("gqa_attention with a norm over the whole projection cannot run on another layer's cache")
+        qkv = torch.empty((T, (H + (1 if self.v_from_k else 2) * g_here) * hd), dtype=self.act_dtype, device=h.device)
         ops.linear(h, self.wq if reads_only else self.wqkv, qkv)
+        opts = dict(whole_norm=self.whole_norm, v_from_k=self.v_from_k and not reads_only)
         table = ctx.block_tables[cache.group]
         eps = self.qk_norm_eps if self.qk_norm_eps is not None else 0.0
         fused = self.pos.fused_tables(qkv.device) if (self.pos is not None and hasattr(self.pos, "fused_tables")) else None
@@ -74,11 +100,14 @@ class GQAAttention(Mixer):
             inv_freq, rot = fused if fused is not None else (None, 0)
             ops.qk_norm_rope_write(qkv, self.qn, self.kn, inv_freq, ctx.positions, ctx.row_of_token, table,
                                    cache.k_pages, cache.v_pages, H, g_here, hd, rot, eps,
-                                   write_kv=not reads_only)
+                                   write_kv=not reads_only, interleaved=getattr(self.pos, "interleaved", False),
+                                   amplitude=getattr(self.pos, "amplitude", 1.0), **opts)
         else:
             # norm, then the position encoding's own rotation, then the cache write
+            if self.v_from_k:
+                raise ValueError("gqa_attention: values='keys' needs a position encoding with fused tables (or none)")
             ops.qk_norm_rope_write(qkv, self.qn, self.kn, None, ctx.positions, ctx.row_of_token, None, None, None,
-                                   H, g_here, hd, 0, eps, write_kv=False)
+                                   H, g_here, hd, 0, eps, write_kv=False, whole_norm=self.whole_norm)
             q3 = qkv[:, : H * hd].unflatten(1, (H, hd))
             k3 = None if reads_only else qkv[:, H * hd:(H + G) * hd].unflatten(1, (G, hd))
             self.pos.rotate(ctx, q3, k3)
@@ -87,5 +116,6 @@ class GQAAttention(Mixer):
                                        cache.k_pages, cache.v_pages, H, G, hd, 0, 0.0, write_kv=True)
         att = torch.empty((T, H * hd), dtype=self.act_dtype, device=qkv.device)
         ops.paged_attention(qkv, cache.k_pages, cache.v_pages, table, ctx.positions, ctx.row_of_token, att,
-                            H, G, hd, self.scale, self.window or 0, ctx=ctx)
+                            H, G, hd, self.scale, self.window or 0, ctx=ctx, chunk=self.chunk or 0, sink=self.sink,
+                            out_scale=self.out_scale)
         ops.linear(att, self.wo, residual, accumulate=True)

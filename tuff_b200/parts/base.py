@@ -50,11 +50,14 @@ class WeightDecl:
 class PagedKVNeed:
     """Keys and values that grow with the tokens; `window` = how many of the
     latest keys a token may see (None: all of them).  `v_head_dim`: the width of a value where it
-    differs from a key's (the pages of V are then `[pages, kv_heads, page_size, v_head_dim]`)."""
+    differs from a key's (the pages of V are then `[pages, kv_heads, page_size, v_head_dim]`).
+    `chunk`: a token sees only the keys of its own chunk of this many positions, counted from
+    position 0 (None: no such bound); pages that lie wholly before the next token's chunk go back."""
     kv_heads: int
     head_dim: int
     window: int | None = None
     v_head_dim: int | None = None
+    chunk: int | None = None
 
 
 @dataclass(frozen=True)
@@ -64,6 +67,13 @@ class StateNeed:
     shape: Tuple[int, ...]
     dtype: str = "float32"
     fill: float = 0.0
+
+
+@dataclass(frozen=True)
+class CompositeNeed:
+    """Several needs of one mixer (keys and values in pages beside a fixed-size state, say); the mixer's
+    storage is then a `CompositeStorage` whose `parts` follow the order given here."""
+    parts: Tuple[object, ...]
 
 
 @dataclass
@@ -110,7 +120,7 @@ class PositionEncoding(Part):
 
 
 class Mixer(Part):
-    def cache_need(self) -> PagedKVNeed | StateNeed | None:
+    def cache_need(self) -> "PagedKVNeed | StateNeed | CompositeNeed | None":
         return None
 
     def forward(self, ctx, cache, h, residual, reads_only: bool = False) -> None:

@@ -1,8 +1,13 @@
 """Arrangements of a layer's parts.  `prenorm`: x += mixer(norm_a(x)), then
 x += ffn(norm_b(x)), the residual stream staying in fp32 throughout
-(reference: src/lfm25_engine.c:365-423)."""
+(reference: src/lfm25_engine.c:365-423).  `postnorm`: the norm comes after the
+sum, x <- norm_a(alpha * x + mixer(x)), then x <- norm_b(alpha * x + ffn(x)); the
+sublayers read x itself; a layer without feed-forward ends after the first."""
 from __future__ import annotations
 
+import torch
+
+from ..kernels import ops
 from .base import Block, register_block
 
 
@@ -18,3 +23,31 @@ class PreNormBlock(Block):
         if next_norm is not None:
             next_norm.announce(ctx, x)
         layer.ffn.forward(ctx, h, x)
+
+
+@register_block("postnorm")
+class PostNormBlock(Block):
+    """The stream x is kept in three views (see `RMSNorm.fork`): x itself in fp32, h = x in the activation
+    dtype for the products, s = alpha * x in fp32 for the addition; each norm writes all three in one
+    kernel, and the pair (h, s) a layer ends with is handed to the next layer through `ctx.extra`."""
+
+    def __init__(self, alpha: float = 1.0):
+        self.alpha = float(alpha)
+
+    def forward(self, ctx, x, layer, cache, reads_only=False, next_norm=None):
+        ready = ctx.extra.pop("postnorm_views", None)
+        if ready is not None and ready[0] is x and ready[1] == x._version and ready[2] == self.alpha:
+            h, s = ready[3], ready[4]
+        else:
+            s = torch.empty_like(x)
+            h = x if ctx.act_dtype == torch.float32 else torch.empty(x.shape, dtype=ctx.act_dtype, device=x.device)
+            ops.stream_fork(x, self.alpha, None if h is x else h, s)
+        layer.mixer.forward(ctx, cache, h, s, reads_only)
+        if layer.ffn is not None:
+            h, s = layer.mixer_norm.fork(ctx, s, self.alpha)
+            layer.ffn.forward(ctx, h, s)
+            last = layer.ffn_norm
+        else:
+            last = layer.mixer_norm
+        h, s = last.fork(ctx, s, self.alpha, x_out=x)
+        ctx.extra["postnorm_views"] = (x, x._version, self.alpha, h, s)

@@ -25,6 +25,23 @@ class TokenEmbedding(Embedding):
         return x
 
 
+@register_embedding("token_position_embedding")
+class TokenPositionEmbedding(Embedding):
+    """x = E[token] + P[position]: a learned vector per position, added unscaled.  The model's context is
+    bounded by the number of position vectors."""
+
+    def __init__(self, vocab_size: int, d_model: int, max_positions: int):
+        self.V, self.d, self.P = int(vocab_size), int(d_model), int(max_positions)
+
+    def weight_decls(self):
+        return {"weight": WeightDecl((self.V, self.d)), "positions": WeightDecl((self.P, self.d))}
+
+    def forward(self, ctx):
+        x = torch.empty((ctx.n_tokens, self.d), dtype=torch.float32, device=ctx.device)
+        ops.embed(ctx.tokens, self.w["weight"], x, ctx.positions, self.w["positions"])
+        return x
+
+
 @register_head("lm_head")
 class LMHead(Head):
     def __init__(self, vocab_size: int, d_model: int):

@@ -31,3 +31,17 @@ class RMSNorm(Norm):
         out = torch.empty((n, self.dim), dtype=self.act_dtype, device=x.device)
         ops.rmsnorm(x, self.w["weight"], self.eps, out, row_index)
         return out
+
+    def fork(self, ctx, s, alpha: float, x_out=None, want_stream: bool = True):
+        """For a layer that norms after the sum: `s` (fp32 [T, d]) holds alpha * x_old + f(x_old).  Writes
+        x = rmsnorm(s) * w into `x_out` (fp32, if given) and returns (h, s_next): h = x in the activation dtype
+        for the next sublayer's products (x_out itself in the 32-bit engine) and s_next = alpha * x, written over
+        `s`, for its addition (None if `want_stream` is False)."""
+        if self.act_dtype == torch.float32:
+            if x_out is None:
+                x_out = torch.empty_like(s)
+            h, h_out = x_out, None
+        else:
+            h = h_out = torch.empty(s.shape, dtype=self.act_dtype, device=s.device)
+        ops.rmsnorm_fork(s, self.w["weight"], self.eps, alpha, x_out, h_out, s if want_stream else None, self.act_dtype)
+        return h, (s if want_stream else None)

@@ -18,6 +18,9 @@ from .base import PositionEncoding, register_position_encoding
 
 @register_position_encoding("rope_neox")
 class RotaryNeox(PositionEncoding):
+    interleaved = False      # which elements form a pair: (i, i + span/2), or (2i, 2i+1) when True
+    amplitude = 1.0          # factor on cos and sin
+
     def __init__(self, head_dim: int, theta: float, rotary_dim: int | None = None):
         self.head_dim = int(head_dim)
         self.theta = float(theta)
@@ -35,3 +38,40 @@ class RotaryNeox(PositionEncoding):
         if self._inv_freq is None or self._inv_freq.device != torch.device(device):
             self._inv_freq = torch.from_numpy(self.inv_freq_host()).to(device)
         return self._inv_freq, self.rotary_dim
+
+
+@register_position_encoding("rope_yarn")
+class RotaryYarn(RotaryNeox):
+    """Rotary encoding with YaRN frequency scaling.  Base frequencies f_i = theta^(-2i/span), i < span/2.
+    With d(t) = span * ln(original / (2 pi t)) / (2 ln theta), lo = max(floor(d(fast)), 0),
+    hi = min(ceil(d(slow)), span - 1) and ramp_i = clamp((i - lo) / max(hi - lo, 0.001), 0, 1), pair i turns
+    by pos * (f_i / factor * ramp_i + f_i * (1 - ramp_i)), and cos and sin are multiplied by the amplitude
+    0.1 ln(factor) + 1.  `pairing`: "interleaved" pairs element 2i with 2i+1, "neox" pairs i with i + span/2.
+    Without `factor` it is the plain rotation with the chosen pairing."""
+
+    def __init__(self, head_dim: int, theta: float, rotary_dim: int | None = None, pairing: str = "interleaved",
+                 factor: float | None = None, original: float | None = None, fast: float | None = None,
+                 slow: float | None = None):
+        super().__init__(head_dim, theta, rotary_dim)
+        if pairing not in ("interleaved", "neox"):
+            raise ValueError(f"rope_yarn: pairing {pairing!r}; choose interleaved or neox")
+        self.interleaved = pairing == "interleaved"
+        self.factor = None if factor is None else float(factor)
+        if self.factor is not None:
+            if original is None or fast is None or slow is None:
+                raise ValueError("rope_yarn with a factor needs original, fast and slow")
+            self.original, self.fast, self.slow = float(original), float(fast), float(slow)
+        self.amplitude = 1.0 if self.factor is None else 0.1 * float(np.log(self.factor)) + 1.0
+
+    def inv_freq_host(self) -> np.ndarray:
+        n = self.rotary_dim
+        i = np.arange(n // 2, dtype=np.float64)
+        f = self.theta ** (-2.0 * i / n)
+        if self.factor is not None:
+            def at(turns):
+                return n * np.log(self.original / (2.0 * np.pi * turns)) / (2.0 * np.log(self.theta))
+            lo = max(np.floor(at(self.fast)), 0.0)
+            hi = min(np.ceil(at(self.slow)), n - 1.0)
+            ramp = np.clip((i - lo) / max(hi - lo, 0.001), 0.0, 1.0)
+            f = f / self.factor * ramp + f * (1.0 - ramp)
+        return f.astype(np.float32)
