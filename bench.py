@@ -25,6 +25,10 @@ Peaks come from MEASURED_PEAKS.json beside this file when it exists, else the fa
 For more than one GPU it prints one line that says so and exits with 2: the engine is
 single-GPU.  `--impl reference` answers that the reference cannot run here.
 `--print-config NAME` prints one of the shapes below as a config.json and exits.
+`--design koridra` leaves all of that alone and prints another line instead: the Koridra design at two
+sizes (random weights) beside the LFM2 shape of the same width, depth and feed-forward, each with
+a 2,048-token prompt in one step and decode steps at batch 1, 8 and 64 (context 2,048), tokens a second
+from device time, and for decode the fraction of the step's HBM bound.
 """
 from __future__ import annotations
 
@@ -54,6 +58,28 @@ SHAPES = {
                       block_auto_adjust_ff_dim=True, full_attn_idxs=[2, 5, 8, 10, 12, 14]),
     "lfm2-2.6b": dict(_LFM2, hidden_size=2048, num_hidden_layers=30, num_attention_heads=32, intermediate_size=10752,
                       block_auto_adjust_ff_dim=True, full_attn_idxs=[2, 6, 10, 14, 18, 21, 24, 27]),
+}
+
+
+
+def koridra_shape(width, layers, ff, heads, parallel_at, vocab=65536, max_positions=8192):
+    """A Koridra configuration of a real model's proportions: lightning layers with `heads` heads of 128 x 128
+    (inner width = `width`), and at `parallel_at` a softmax branch (heads of 128 in groups of four, a chunk of
+    2,048 positions, half of each head rotated, YaRN) beside a gated linear branch of half the heads."""
+    decay = [1.0 - 2.0 ** (-5.0 - 4.0 * h / max(1, heads - 1)) for h in range(heads)]
+    light = dict(type="lightning", mixer=dict(heads=heads, dim=128, vdim=128, decay=decay), mlp=dict(kind="dense", ff=ff))
+    par = dict(type="parallel", mlp=dict(kind="dense", ff=ff), mixer=dict(
+        left=dict(heads=heads, kv_heads=max(1, heads // 4), dim=128, vdim=128, scale=128 ** -0.5, mask=dict(size=2048),
+                  rot=dict(dims=64, base=1e6, scaling=dict(factor=8.0, original=1024, fast=32.0, slow=1.0))),
+        right=dict(heads=max(1, heads // 2), dim=128, vdim=128, tau=16.0, gate_rank=64), left_scale=0.6, right_scale=1.1))
+    return dict(architecture="Koridra", vocab=vocab, width=width, max_positions=max_positions, norm=dict(eps=1e-5),
+                postln_alpha=3.0, layers=[par if i in parallel_at else light for i in range(layers)])
+
+
+# Koridra sizes beside the LFM2 shape of equal width, depth and feed-forward width
+KORIDRA_PAIRS = {
+    "1.2b": (koridra_shape(2048, 16, 5632, 16, (3, 7, 11, 15)), "lfm2.5-1.2b"),
+    "350m": (koridra_shape(1024, 16, 4608, 8, (3, 7, 11, 15)), "lfm2-350m"),
 }
 
 CONTEXT = 8192
@@ -309,6 +335,87 @@ def serve_point(points, name, engine, rng, n_requests=64, runs=RUNS):
     points[name + "_host_share"] = round(sum(host) / len(host), 3)
 
 
+def generic_numbers(cfg_dict):
+    """For any registered design: bytes of weights a decode step reads (every tensor once, the embedding
+    tables excepted, of which a step gathers rows), bytes of keys and values per cached token, bytes of
+    state per request, and the matmul parameters."""
+    import math
+    from tuff_b200.config import config_from_dict
+    from tuff_b200.models import Model
+    from tuff_b200.parts.base import CompositeNeed, PagedKVNeed, StateNeed
+    arch, cfg = config_from_dict(cfg_dict)
+    model = Model(arch.model_spec(cfg))
+    exp = model.expected_tensors()
+    gathered = set(model.spec.embedding.tensors.values()) - set(model.spec.head.tensors.values())
+    weight_bytes = sum(math.prod(d.shape) * (4 if d.role == "vector" else 2) for n, d in exp.items() if n not in gathered)
+    matmul = sum(math.prod(d.shape) for n, d in exp.items() if d.role == "matrix" and len(d.shape) == 2 and n not in gathered)
+    kv = state = 0
+    chunk = None
+
+    def walk(need):
+        nonlocal kv, state, chunk
+        if isinstance(need, CompositeNeed):
+            for n in need.parts:
+                walk(n)
+        elif isinstance(need, PagedKVNeed):
+            kv += need.kv_heads * (need.head_dim + (need.v_head_dim or need.head_dim)) * 2
+            chunk = need.chunk or need.window or chunk
+        elif isinstance(need, StateNeed):
+            state += math.prod(need.shape) * 4
+    for need in model.storage_needs():
+        walk(need)
+    return cfg, dict(weight_bytes=weight_bytes, matmul_params=matmul, kv_bytes_per_token=kv, state_bytes=state,
+                     kv_span=chunk, vocab=model.spec.vocab_size, d=model.spec.d_model)
+
+
+def compare_designs(args) -> int:
+    """`--design koridra`: see the module's docstring."""
+    import numpy as np
+    import torch
+    from tuff_b200.engine.engine import Engine
+    pk, pk_src = peaks()
+    rng = np.random.default_rng(0)
+    steps, warmup = max(1, min(args.steps, 32)), max(3, args.warmup)
+    context = 2048
+    sampler = ClockSampler()
+    sampler.start()
+    out = {}
+    for size, (kor, lfm_name) in KORIDRA_PAIRS.items():
+        if args.sizes and size not in args.sizes.split(","):
+            continue
+        for label, cfg_dict in (("koridra", kor), ("lfm2", SHAPES[lfm_name])):
+            cfg, nums = generic_numbers(cfg_dict)
+            eng = Engine(None, dtype="bfloat16", ctx_size=context, max_tokens=64 * context + 4096, page_size=PAGE,
+                         max_batched_tokens=PREFILL_TOKENS, max_running=64, config=cfg_dict, weight_seed=0)
+            eng.runner.randomize_cache(1)
+            res = {"weight_mb": round(nums["weight_bytes"] / 1e6, 1), "state_kb_per_request": round(nums["state_bytes"] / 1e3, 1),
+                   "kv_bytes_per_token": nums["kv_bytes_per_token"]}
+            secs = measure_prefill(eng.runner, cfg, rng, PREFILL_TOKENS, PREFILL_TOKENS)
+            ms = sum(secs) / len(secs) * 1e3
+            # matrices alone: the flops every design of this size has to do on the tensor cores
+            flops = 2.0 * (nums["matmul_params"] - nums["vocab"] * nums["d"]) * PREFILL_TOKENS + 2.0 * nums["vocab"] * nums["d"]
+            res["prefill_2048_tok_s"] = round(PREFILL_TOKENS / ms * 1e3, 1)
+            res["prefill_2048_ms"] = round(ms, 3)
+            res["prefill_matrix_frac"] = round(flops / (ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)
+            for b in (1, 8, 64):
+                dev_s, _, launches, ctx_mid = measure_decode(eng, b, context, steps, warmup, rng, genuine_prefill=(b == 1))
+                v, pm = mean_pm([b * steps / t for t in dev_s])
+                seen = min(ctx_mid, nums["kv_span"]) if nums["kv_span"] else ctx_mid
+                bytes_ = nums["weight_bytes"] + b * (seen * nums["kv_bytes_per_token"] + 2 * nums["state_bytes"])
+                res[f"decode_b{b}_tok_s"] = round(v, 1)
+                res[f"decode_b{b}_pm"] = round(pm, 1)
+                res[f"decode_b{b}_ms"] = round(b / v * 1e3, 4)
+                res[f"decode_b{b}_hbm_frac"] = round(bytes_ / (b / v) / 1e9 / pk["hbm_gbs"], 4)
+                res[f"decode_b{b}_launches_per_step"] = round(launches / (RUNS * steps), 1)
+            out[f"{label}_{size}"] = res
+            del eng
+            torch.cuda.empty_cache()
+    print(json.dumps({"design": "koridra beside lfm2 at equal width, depth and feed-forward", "dtype": "bf16",
+                      "data": "synthetic (random bf16 weights, uniform random token ids)", "context": context,
+                      "steps": steps, "warmup": warmup, "runs": RUNS, "peaks": pk_src, "clocks": sampler.stop(), "results": out}))
+    return 0
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -318,6 +425,9 @@ def main() -> int:
     ap.add_argument("--layers", type=int, default=None, help="fewer layers than the configuration has (recorded)")
     ap.add_argument("--no-points", action="store_true", help="the headline only: no prefill, no other points")
     ap.add_argument("--print-config", choices=sorted(SHAPES), default=None, help="print a shape as a config.json and exit")
+    ap.add_argument("--design", choices=["koridra"], default=None,
+                    help="instead of the default workload: this design beside the LFM2 shape of equal size")
+    ap.add_argument("--sizes", default="", help="with --design: which of the sizes (1.2b,350m), with commas; default all")
     args = ap.parse_args()
     if args.print_config:
         print(json.dumps(SHAPES[args.print_config], indent=1))
@@ -330,6 +440,8 @@ def main() -> int:
     if args.gpus != 1:
         print(json.dumps({"error": "tuff_b200 is a single-GPU engine: run with --gpus 1", "n_gpus": args.gpus}))
         return 2
+    if args.design:
+        return compare_designs(args)
     warmup = max(3, args.warmup)
     steps = max(1, args.steps)
 

@@ -144,6 +144,10 @@ struct AttnParams {
     float* part_o; float* part_ml;   // decode: [T, H, splits, HD] and [T, H, splits, 2]
     int* status;
     int n_tokens, n_rows, H, G, page_size, window, n_splits;
+    int chunk;                       // > 0: a query sees only the keys of its own chunk of this many positions
+    int has_sink;                    // the softmax has one more score, without a value
+    float sink_log2;                 // that score, in the units of scale_log2
+    float out_scale;                 // factor on the result
     float scale_log2;
 };
 
@@ -198,7 +202,7 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap mk, const __grid_constant
     pdl_wait();                                   // everything below reads what earlier kernels wrote
     const int pos = ld_act(p.positions + tok);
     const int row = ld_act(p.row_of_token + tok);
-    const int lo = (p.window > 0 && pos - p.window + 1 > 0) ? pos - p.window + 1 : 0;
+    const int lo = first_key(pos, p.window, p.chunk);
     const int tile_lo = lo / TILE, tile_hi = pos / TILE;
     const int n_tiles = tile_hi - tile_lo + 1;
     const int per = (n_tiles + p.n_splits - 1) / p.n_splits;
@@ -271,7 +275,11 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap mk, const __grid_constant
         }
         const int h = g * HG + r;
         if (p.n_splits == 1) {
-            p.out[((size_t)tok * p.H + h) * HD + d] = __float2bfloat16_rn(L > 0.f ? O / L : 0.f);
+            if (p.has_sink) {                     // the sink joins the denominator once, where the sums are complete
+                const float M2 = fmaxf(M, p.sink_log2), f = M == -INFINITY ? 0.f : exp2f(M - M2);
+                L = L * f + exp2f(p.sink_log2 - M2); O *= f;
+            }
+            p.out[((size_t)tok * p.H + h) * HD + d] = __float2bfloat16_rn(L > 0.f ? O / L * p.out_scale : 0.f);
         } else {
             const size_t pi = ((size_t)tok * p.H + h) * p.n_splits + split;
             p.part_o[pi * HD + d] = O;
@@ -282,22 +290,23 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap mk, const __grid_constant
 
 template <int HD>
 __global__ void attn_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
-                                    bf16* __restrict__ out, int n_splits) {
+                                    bf16* __restrict__ out, int n_splits, int has_sink, float sink_log2, float out_scale) {
     const size_t th = blockIdx.x;                      // token * H + head
     pdl_wait();
     pdl_launch_dependents();
     const float* ml = part_ml + th * n_splits * 2;
     float M = -INFINITY;
     for (int s = 0; s < n_splits; ++s) M = fmaxf(M, ld_act(ml + 2 * s));
+    if (has_sink) M = fmaxf(M, sink_log2);
     for (int d = threadIdx.x; d < HD; d += blockDim.x) {
-        float L = 0.f, O = 0.f;
+        float L = has_sink ? exp2f(sink_log2 - M) : 0.f, O = 0.f;
         for (int s = 0; s < n_splits; ++s) {
             const float ms = ld_act(ml + 2 * s);
             const float f = ms == -INFINITY ? 0.f : exp2f(ms - M);
             L += ld_act(ml + 2 * s + 1) * f;
             O += ld_act(part_o + (th * n_splits + s) * HD + d) * f;
         }
-        out[th * HD + d] = __float2bfloat16_rn(L > 0.f ? O / L : 0.f);
+        out[th * HD + d] = __float2bfloat16_rn(L > 0.f ? O / L * out_scale : 0.f);
     }
 }
 
@@ -332,7 +341,7 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap mk, const __grid_constan
     const int n_here = min(QTOK, q1 - q0);
     const int pos0 = p.positions[q0];             // positions of a row's tokens are consecutive
     const int pos_last = pos0 + n_here - 1;
-    const int lo_cta = (p.window > 0 && pos0 - p.window + 1 > 0) ? pos0 - p.window + 1 : 0;
+    const int lo_cta = first_key(pos0, p.window, p.chunk);
     const int tile_lo = lo_cta / TILE, tile_hi = pos_last / TILE;
     const int n_tiles = tile_hi - tile_lo + 1;
     const int* bt = p.block_table + (size_t)row * p.max_blocks;
@@ -359,10 +368,10 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap mk, const __grid_constan
         const bool va = tok_a < q1 && sub * 16 + g_lane < n_here, vb = tok_b < q1 && sub * 16 + g_lane + 8 < n_here;
         const int pos_a = pos0 + sub * 16 + g_lane, pos_b = pos_a + 8;
         const int hi_a = va ? pos_a : -1, hi_b = vb ? pos_b : -1;
-        const int lo_a = (p.window > 0 && pos_a - p.window + 1 > 0) ? pos_a - p.window + 1 : 0;
-        const int lo_b = (p.window > 0 && pos_b - p.window + 1 > 0) ? pos_b - p.window + 1 : 0;
+        const int lo_a = first_key(pos_a, p.window, p.chunk);
+        const int lo_b = first_key(pos_b, p.window, p.chunk);
         const int warp_hi = min(pos_last, pos0 + sub * 16 + 15);           // last key any row of this warp sees
-        const int warp_lo = (p.window > 0 && pos0 + sub * 16 - p.window + 1 > 0) ? pos0 + sub * 16 - p.window + 1 : 0;
+        const int warp_lo = first_key(pos0 + sub * 16, p.window, p.chunk);
         const bool warp_live = sub * 16 < n_here;
         uint32_t qa[Frag<HD>::KS][4];
         const bf16* qa_row = p.q + (size_t)(va ? tok_a : q0) * p.q_stride + (size_t)h * HD;
@@ -384,7 +393,7 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap mk, const __grid_constan
             const int key0 = (tile_lo + i) * TILE;
             if (warp_live && key0 <= warp_hi && key0 + TILE - 1 >= warp_lo) {
                 // masks are needed unless every row of the warp sees the whole tile
-                const bool need_mask = key0 + TILE - 1 > pos0 + sub * 16 || (p.window > 0 && key0 < pos0 + sub * 16 + 15 - p.window + 1)
+                const bool need_mask = key0 + TILE - 1 > pos0 + sub * 16 || key0 < first_key(pos0 + sub * 16 + 15, p.window, p.chunk)
                                        || sub * 16 + 15 >= n_here;
                 process_tile<HD>(base + s * STAGE_BYTES, base + s * STAGE_BYTES + TILE * HD * 2, qa, o, m_a, m_b, l_a, l_b,
                                  key0, lo_a, hi_a, lo_b, hi_b, pos_last, p.scale_log2, need_mask);
@@ -394,8 +403,15 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap mk, const __grid_constan
         }
         l_a += __shfl_xor_sync(0xffffffffu, l_a, 1); l_a += __shfl_xor_sync(0xffffffffu, l_a, 2);
         l_b += __shfl_xor_sync(0xffffffffu, l_b, 1); l_b += __shfl_xor_sync(0xffffffffu, l_b, 2);
+        if (p.has_sink) {
+            const float ma = fmaxf(m_a, p.sink_log2), mb = fmaxf(m_b, p.sink_log2);
+            const float fa = m_a == -INFINITY ? 0.f : exp2f(m_a - ma), fb = m_b == -INFINITY ? 0.f : exp2f(m_b - mb);
+            l_a = l_a * fa + exp2f(p.sink_log2 - ma); l_b = l_b * fb + exp2f(p.sink_log2 - mb);
+#pragma unroll
+            for (int dt = 0; dt < Frag<HD>::DT; ++dt) { o[dt][0] *= fa; o[dt][1] *= fa; o[dt][2] *= fb; o[dt][3] *= fb; }
+        }
         if (ok) {
-            const float ia = l_a > 0.f ? 1.f / l_a : 0.f, ib = l_b > 0.f ? 1.f / l_b : 0.f;
+            const float ia = l_a > 0.f ? p.out_scale / l_a : 0.f, ib = l_b > 0.f ? p.out_scale / l_b : 0.f;
             bf16* oa = p.out + ((size_t)tok_a * p.H + h) * HD;
             bf16* ob = p.out + ((size_t)tok_b * p.H + h) * HD;
 #pragma unroll
@@ -461,7 +477,7 @@ extern "C" int tuff_attention_decode(const void* q, long long q_stride, const vo
                                      long long num_pages, const int* block_table, int max_blocks, const int* positions,
                                      const int* row_of_token, void* out, float* workspace, int n_splits, int* status,
                                      int n_tokens, int H, int G, int hd, int page_size, float scale, int window,
-                                     cudaStream_t stream) {
+                                     int chunk, int has_sink, float sink, float out_scale, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (!supported(H, G, hd, page_size) || n_splits < 1) return TUFF_E_SIZE;
     if (((uintptr_t)q & 3) || (q_stride & 1) || ((uintptr_t)k_pages & 127) || ((uintptr_t)v_pages & 127)) return TUFF_E_ALIGN;
@@ -473,6 +489,7 @@ extern "C" int tuff_attention_decode(const void* q, long long q_stride, const vo
     p.positions = positions; p.row_of_token = row_of_token; p.out = (bf16*)out; p.status = status;
     p.part_o = workspace; p.part_ml = workspace ? workspace + (size_t)n_tokens * H * n_splits * hd : nullptr;
     p.n_tokens = n_tokens; p.H = H; p.G = G; p.page_size = page_size; p.window = window; p.n_splits = n_splits;
+    p.chunk = chunk; p.has_sink = has_sink; p.sink_log2 = sink * 1.4426950408889634f; p.out_scale = out_scale;
     p.scale_log2 = scale * 1.4426950408889634f;
     if (n_splits > 1 && !workspace) return TUFF_E_SIZE;
     dim3 grid(n_tokens, G, n_splits);
@@ -490,8 +507,8 @@ extern "C" int tuff_attention_decode(const void* q, long long q_stride, const vo
         rc = launch_pdl(attn_decode_kernel<128>, grid, dim3(threads), smem, stream, mk, mv, p);
     }
     if (rc || (rc = launch_status()) || n_splits == 1) return rc;
-    if (hd == 64) rc = launch_pdl(attn_combine_kernel<64>, dim3(n_tokens * H), dim3(64), 0, stream, (const float*)p.part_o, (const float*)p.part_ml, p.out, n_splits);
-    else rc = launch_pdl(attn_combine_kernel<128>, dim3(n_tokens * H), dim3(128), 0, stream, (const float*)p.part_o, (const float*)p.part_ml, p.out, n_splits);
+    if (hd == 64) rc = launch_pdl(attn_combine_kernel<64>, dim3(n_tokens * H), dim3(64), 0, stream, (const float*)p.part_o, (const float*)p.part_ml, p.out, n_splits, has_sink, p.sink_log2, out_scale);
+    else rc = launch_pdl(attn_combine_kernel<128>, dim3(n_tokens * H), dim3(128), 0, stream, (const float*)p.part_o, (const float*)p.part_ml, p.out, n_splits, has_sink, p.sink_log2, out_scale);
     return rc ? rc : launch_status();
 }
 
@@ -499,7 +516,7 @@ extern "C" int tuff_attention_prefill(const void* q, long long q_stride, const v
                                       long long num_pages, const int* block_table, int max_blocks, const int* positions,
                                       const int* row_of_token, const int* cu_q, void* out, int* status, int n_tokens,
                                       int n_rows, int H, int G, int hd, int page_size, float scale, int window,
-                                      cudaStream_t stream) {
+                                      int chunk, int has_sink, float sink, float out_scale, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (!supported(H, G, hd, page_size)) return TUFF_E_SIZE;
     if (((uintptr_t)q & 3) || (q_stride & 1) || ((uintptr_t)k_pages & 127) || ((uintptr_t)v_pages & 127)) return TUFF_E_ALIGN;
@@ -510,6 +527,7 @@ extern "C" int tuff_attention_prefill(const void* q, long long q_stride, const v
     p.q = (const bf16*)q; p.q_stride = q_stride; p.block_table = block_table; p.max_blocks = max_blocks; p.n_pages = num_pages;
     p.positions = positions; p.row_of_token = row_of_token; p.cu_q = cu_q; p.out = (bf16*)out; p.status = status;
     p.n_tokens = n_tokens; p.n_rows = n_rows; p.H = H; p.G = G; p.page_size = page_size; p.window = window; p.n_splits = 1;
+    p.chunk = chunk; p.has_sink = has_sink; p.sink_log2 = sink * 1.4426950408889634f; p.out_scale = out_scale;
     p.scale_log2 = scale * 1.4426950408889634f;
     const int HG = H / G, QTOK = 16 * (PRE_WARPS / HG);
     dim3 grid((n_tokens + QTOK - 1) / QTOK + n_rows, G);       // an upper bound on the blocks of all rows

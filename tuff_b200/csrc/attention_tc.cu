@@ -50,6 +50,8 @@ struct TcAttnParams {
     bf16* out;
     int* status;
     int n_rows, H, G, page_size, window, n_blocks;
+    int chunk, has_sink;             // keys of the query's own chunk of positions only; one more score without a value
+    float sink_log2, out_scale;      // that score in the units of scale_log2; factor on the result
     float scale_log2;
 };
 
@@ -128,7 +130,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap mk, const __grid_cons
     const int n_here = min(QROWS, q1 - q0);
     const int pos0 = ld_act(p.positions + q0);     // positions of a request's tokens are consecutive
     const int pos_last = pos0 + n_here - 1;
-    const int lo_cta = (p.window > 0 && pos0 - p.window + 1 > 0) ? pos0 - p.window + 1 : 0;
+    const int lo_cta = first_key(pos0, p.window, p.chunk);
     const int tile_lo = lo_cta / TILE, tile_hi = pos_last / TILE;
     const int n_tiles = tile_hi - tile_lo + 1;
     const int* bt = p.block_table + (size_t)row * p.max_blocks;
@@ -216,9 +218,9 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap mk, const __grid_cons
         const bool valid = r < n_here;
         const int pos_r = pos0 + r;
         const int hi_r = valid ? pos_r : -1;
-        const int lo_r = (p.window > 0 && pos_r - p.window + 1 > 0) ? pos_r - p.window + 1 : 0;
+        const int lo_r = first_key(pos_r, p.window, p.chunk);
         const int w_first = pos0 + warp * 32, w_last = min(pos_last, w_first + 31);
-        const int warp_lo = (p.window > 0 && w_first - p.window + 1 > 0) ? w_first - p.window + 1 : 0;
+        const int warp_lo = first_key(w_first, p.window, p.chunk);
         const bool warp_valid = warp * 32 < n_here;
         const uint32_t lane_addr = (uint32_t)(warp * 32) << 16;
         {   // this row of Q into shared memory (zeros beyond the portion)
@@ -257,7 +259,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap mk, const __grid_cons
             }
             float mx = -INFINITY;
             if (live) {
-                const bool need_mask = key0 + TILE - 1 > w_first || (p.window > 0 && key0 < w_first + 31 - p.window + 1) ||
+                const bool need_mask = key0 + TILE - 1 > w_first || key0 < first_key(w_first + 31, p.window, p.chunk) ||
                                        warp * 32 + 31 >= n_here;
                 float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};       // four chains, not one of 64
                 if (need_mask) {                                                    // uniform over the warp
@@ -323,7 +325,9 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap mk, const __grid_cons
         if (ok && !mbar_wait(pv_full((n_tiles - 1) & 1), ((n_tiles - 1) >> 1) & 1, p.status, 41)) ok = false;
         tc_fence_after();
         if (ok && warp_valid) {
-            const float inv = l > 0.f ? 1.f / l : 0.f;
+            // the sink's share, in the units of the row's reference maximum like l and O
+            if (p.has_sink && m_ref != -INFINITY) l += ex2(p.sink_log2 - m_ref * p.scale_log2);
+            const float inv = l > 0.f ? p.out_scale / l : 0.f;
             bf16* orow = p.out + ((size_t)(q0 + r) * p.H + h) * HD;
 #pragma unroll
             for (int d0 = 0; d0 < HD; d0 += 32) {
@@ -369,7 +373,8 @@ extern "C" int tuff_attention_prefill_tc_supported(int H, int G, int hd, int pag
 extern "C" int tuff_attention_prefill_tc(const void* q, long long q_stride, const void* k_pages, const void* v_pages,
                                          long long num_pages, const int* block_table, int max_blocks, const int* positions,
                                          const int* cu_q, void* out, int* status, int n_tokens, int n_rows, int H, int G,
-                                         int hd, int page_size, float scale, int window, cudaStream_t stream) {
+                                         int hd, int page_size, float scale, int window, int chunk, int has_sink,
+                                         float sink, float out_scale, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (!supported(H, G, hd, page_size)) return TUFF_E_SIZE;
     if (((uintptr_t)q & 15) || (q_stride & 7) || ((uintptr_t)out & 15) || ((uintptr_t)k_pages & 127) || ((uintptr_t)v_pages & 127))
@@ -381,6 +386,7 @@ extern "C" int tuff_attention_prefill_tc(const void* q, long long q_stride, cons
     p.q = (const bf16*)q; p.q_stride = q_stride; p.block_table = block_table; p.max_blocks = max_blocks; p.n_pages = num_pages;
     p.positions = positions; p.cu_q = cu_q; p.out = (bf16*)out; p.status = status;
     p.n_rows = n_rows; p.H = H; p.G = G; p.page_size = page_size; p.window = window;
+    p.chunk = chunk; p.has_sink = has_sink; p.sink_log2 = sink * 1.4426950408889634f; p.out_scale = out_scale;
     p.n_blocks = (n_tokens + QROWS - 1) / QROWS + n_rows;      // an upper bound on the blocks of all requests
     p.scale_log2 = scale * 1.4426950408889634f;
     const int smem = Smem<64>::TOTAL;

@@ -232,7 +232,9 @@ extern "C" int tuff_rmsnorm_fork(const float* s_in, const float* w, float eps, f
                                  int h_dtype, float* s_out, int n_rows, int d, cudaStream_t stream) {
     if (n_rows <= 0) return 0;
     auto al16 = [](const void* p) { return !((uintptr_t)p & 15); };
-    if (h_dtype == TUFF_BF16 && n_rows > 16 && d % 4 == 0 && d <= 128 * RMS_VEC && al16(s_in) && al16(w) && al16(x_out) &&
+    // bf16 engine: a warp per row with the row in registers, for any number of rows (the 32-bit engine keeps the
+    // block-per-row kernel, whose order of additions does not depend on the batch)
+    if (h_dtype == TUFF_BF16 && d % 4 == 0 && d <= 128 * RMS_VEC && al16(s_in) && al16(w) && al16(x_out) &&
         al16(s_out) && !((uintptr_t)h_out & 7)) {
         const int warps = n_rows >= 2048 ? 8 : n_rows >= 512 ? 4 : n_rows >= 128 ? 2 : 1;
         return launch_pdl(rmsnorm_fork_rows_kernel, dim3(ceil_div(n_rows, warps)), dim3(32 * warps), 0, stream, s_in, w, eps, alpha,

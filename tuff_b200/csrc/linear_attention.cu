@@ -11,18 +11,17 @@
 // recurrence runs on FFMA.  q, k and v come from the projections in the activation dtype; an
 // activation (silu) and a scale of q are applied when a token's vectors are staged.
 //
-// One CTA owns (batch row, head, 32 value columns) and walks the row's tokens in order; a thread owns
-// one value column and every fourth group of four key channels, so a token costs it dk/4 fused
-// multiply-adds on state in registers and two shuffles.  Tokens are staged through shared memory 16 (8 for the widest heads) at
-// a time (activation, decay and scale computed once per element there).  The order of all sums depends on
-// the sizes only: a request's state and outputs are the same bits however its tokens were cut into steps.
+// One CTA owns (batch row, head, 16 or 32 value columns) and walks the row's tokens in order; a thread owns
+// one value column and every eighth (fourth) group of four key channels, so a token costs it dk/8 (dk/4) state
+// elements in registers and three (two) shuffles.  Tokens are staged through shared memory 16 at a time
+// (activation, decay and scale computed once per element there); the next stage's loads are issued into
+// registers before the current stage is computed.  The order of all sums depends on the sizes only: a request's
+// state and outputs are the same bits however its tokens were cut into steps or batched.
 #include "common.cuh"
 #include "index.cuh"
 
 namespace {
-constexpr int LA_THREADS = 128;         // 4 warps: 32 value columns x 4 key-channel groups
-constexpr int LA_COLS = 32;
-constexpr int LA_KG = 4;
+constexpr int LA_THREADS = 128;         // 4 warps: value columns x threads that share a column
 
 enum { LA_DECAY_HEAD = 0, LA_DECAY_CHANNEL = 1 };
 
@@ -49,20 +48,55 @@ __device__ __forceinline__ float log_sigmoid(float z) {
     return fminf(z, 0.f) - log1pf(expf(-fabsf(z)));
 }
 
-// NC: groups of four key channels a thread owns (dk <= 16 * NC)
-template <typename T, int NC, int MODE>
+// Eight consecutive elements of a token's vector as they lie in memory: loaded early, unpacked late, so
+// that the loads of the next stage are in flight while this stage is computed.
+template <typename T> struct Raw8;
+template <> struct Raw8<bf16> { uint4 v; };
+template <> struct Raw8<float> { float4 a, b; };
+
+__device__ __forceinline__ void load8(Raw8<bf16>& r, const bf16* p, bool vec, int n_valid) {
+    if (vec) { r.v = ld_act_u4(p); return; }
+    unsigned short h[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) h[e] = e < n_valid ? __ldcg(reinterpret_cast<const unsigned short*>(p) + e) : (unsigned short)0;
+    r.v = make_uint4(h[0] | (uint32_t)h[1] << 16, h[2] | (uint32_t)h[3] << 16, h[4] | (uint32_t)h[5] << 16, h[6] | (uint32_t)h[7] << 16);
+}
+__device__ __forceinline__ void load8(Raw8<float>& r, const float* p, bool vec, int n_valid) {
+    if (vec) { r.a = __ldcg(reinterpret_cast<const float4*>(p)); r.b = __ldcg(reinterpret_cast<const float4*>(p) + 1); return; }
+    float f[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) f[e] = e < n_valid ? __ldcg(p + e) : 0.f;
+    r.a = make_float4(f[0], f[1], f[2], f[3]); r.b = make_float4(f[4], f[5], f[6], f[7]);
+}
+__device__ __forceinline__ void unpack8(const Raw8<bf16>& r, float (&f)[8]) {
+    const uint32_t w[4] = {r.v.x, r.v.y, r.v.z, r.v.w};
+#pragma unroll
+    for (int e = 0; e < 4; ++e) { f[2 * e] = __uint_as_float(w[e] << 16); f[2 * e + 1] = __uint_as_float(w[e] & 0xffff0000u); }
+}
+__device__ __forceinline__ void unpack8(const Raw8<float>& r, float (&f)[8]) {
+    f[0] = r.a.x; f[1] = r.a.y; f[2] = r.a.z; f[3] = r.a.w; f[4] = r.b.x; f[5] = r.b.y; f[6] = r.b.z; f[7] = r.b.w;
+}
+
+// NC: groups of four key channels a thread owns; KG: threads that share a value column (dk <= 4 * KG * NC).
+// A CTA covers 128 / KG value columns: KG = 4 for batches that fill the GPU with 32-column tiles, KG = 8 (16
+// columns, twice the CTAs, half the work a token costs a thread) for the few long rows of a prompt.
+template <typename T, int NC, int KG, int MODE>
 __global__ void __launch_bounds__(LA_THREADS)
 linear_attention_kernel(LinAttnParams p) {
-    constexpr int DKP = 16 * NC;                         // padded key channels
-    constexpr int LA_STAGE = NC >= 16 ? 8 : 16;          // tokens staged at a time (48 KB of static shared memory at most)
-    __shared__ __align__(16) float sq[LA_STAGE][DKP];
-    __shared__ __align__(16) float sk[LA_STAGE][DKP];
-    __shared__ __align__(16) float sa[MODE == LA_DECAY_CHANNEL ? LA_STAGE : 1][DKP];
-    __shared__ float sv[LA_STAGE][LA_COLS];
-    const int r = blockIdx.x, h = blockIdx.y, col0 = blockIdx.z * LA_COLS;
+    constexpr int DKP = 4 * KG * NC;                     // padded key channels
+    constexpr int COLS = LA_THREADS / KG;                // value columns of this CTA
+    constexpr int TS = DKP >= 256 ? 8 : 16;              // tokens staged at a time (48 KB of static shared memory at most)
+    constexpr int UNITS = TS * DKP / 8;                  // 8-element pieces of a stage's q (and k, and gate)
+    constexpr int UPT = (UNITS + LA_THREADS - 1) / LA_THREADS;
+    constexpr int VPT = (TS * COLS + LA_THREADS - 1) / LA_THREADS;
+    __shared__ __align__(16) float sq[TS][DKP];
+    __shared__ __align__(16) float sk[TS][DKP];
+    __shared__ __align__(16) float sa[MODE == LA_DECAY_CHANNEL ? TS : 1][DKP];
+    __shared__ float sv[TS][COLS];
+    const int r = blockIdx.x, h = blockIdx.y, col0 = blockIdx.z * COLS;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int kg = lane & 3;                              // key-channel group: channels 4 * (kg + 4 * i) .. + 3
-    const int j = warp * 8 + (lane >> 2);                 // value column within the tile
+    const int kg = lane & (KG - 1);                       // key-channel group: channels 4 * (kg + KG * i) .. + 3
+    const int j = warp * (32 / KG) + lane / KG;           // value column within the tile
     const int col = col0 + j;
     const bool col_ok = col < p.dv;
     pdl_wait();
@@ -74,54 +108,101 @@ linear_attention_kernel(LinAttnParams p) {
     const T* q = reinterpret_cast<const T*>(p.q) + (size_t)h * p.dk;
     const T* k = reinterpret_cast<const T*>(p.k) + (size_t)h * p.dk;
     const T* v = reinterpret_cast<const T*>(p.v) + (size_t)h * p.dv;
+    const float* gate = MODE == LA_DECAY_CHANNEL ? p.gate + (size_t)h * p.dk : nullptr;
+    // whole 16-byte pieces may be loaded as such when every piece of every token is aligned
+    const bool vec_qk = p.dk % 8 == 0 && p.q_stride % 8 == 0 && p.k_stride % 8 == 0 &&
+                        !((uintptr_t)q & 15) && !((uintptr_t)k & 15);
+    const bool vec_g = MODE == LA_DECAY_CHANNEL && p.dk % 8 == 0 && p.gate_stride % 4 == 0 && !((uintptr_t)gate & 15);
 
     float st[NC][4];
 #pragma unroll
     for (int i = 0; i < NC; ++i)
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
-            const int c = 4 * (kg + LA_KG * i) + e;
+            const int c = 4 * (kg + KG * i) + e;
             st[i][e] = (col_ok && c < p.dk) ? S[(size_t)c * p.dv + col] : 0.f;
         }
     const float hd = MODE == LA_DECAY_HEAD ? p.head_decay[h] : 1.f;
 
-    for (int base = t0; base < t1; base += LA_STAGE) {
-        const int n = min(LA_STAGE, t1 - base);
-        __syncthreads();                                  // the stage before this one has been read
-        for (int idx = threadIdx.x; idx < n * DKP; idx += LA_THREADS) {
-            const int tt = idx / DKP, c = idx - tt * DKP;
-            const size_t t = (size_t)(base + tt);
-            float qv = 0.f, kv = 0.f, av = 1.f;
-            if (c < p.dk) {
-                qv = ld_act(q + t * p.q_stride + c);
-                kv = ld_act(k + t * p.k_stride + c);
-                if (p.act) { qv = silu_f(qv); kv = silu_f(kv); }
-                qv *= p.q_scale;
+    Raw8<T> rq[UPT], rk[UPT];
+    Raw8<float> rg[MODE == LA_DECAY_CHANNEL ? UPT : 1];
+    float rv[VPT];
+    // the loads of the stage that begins at token `base` (n tokens), into registers
+    auto fetch = [&](int base, int n) {
+#pragma unroll
+        for (int u = 0; u < UPT; ++u) {
+            const int unit = threadIdx.x + u * LA_THREADS;
+            const int tt = unit / (DKP / 8), c = (unit - tt * (DKP / 8)) * 8;
+            const int left = p.dk - c;                     // valid elements of this piece
+            if (unit < UNITS && tt < n && left > 0) {
+                const size_t t = (size_t)(base + tt);
+                load8(rq[u], q + t * p.q_stride + c, vec_qk, left);
+                load8(rk[u], k + t * p.k_stride + c, vec_qk, left);
+                if (MODE == LA_DECAY_CHANNEL) load8(rg[u], gate + t * p.gate_stride + c, vec_g, left);
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < VPT; ++u) {
+            const int idx = threadIdx.x + u * LA_THREADS;
+            const int tt = idx / COLS, c = idx - tt * COLS;
+            rv[u] = (idx < TS * COLS && tt < n && col0 + c < p.dv) ? ld_act(v + (size_t)(base + tt) * p.v_stride + col0 + c) : 0.f;
+        }
+    };
+    // activation, scale and decay once per element, into shared memory
+    auto stage = [&](int n) {
+#pragma unroll
+        for (int u = 0; u < UPT; ++u) {
+            const int unit = threadIdx.x + u * LA_THREADS;
+            const int tt = unit / (DKP / 8), c = (unit - tt * (DKP / 8)) * 8;
+            if (unit >= UNITS || tt >= n) continue;
+            float fq[8], fk[8], fa[8];
+            const int left = p.dk - c;
+            if (left > 0) {
+                unpack8(rq[u], fq); unpack8(rk[u], fk);
+                if (MODE == LA_DECAY_CHANNEL) unpack8(rg[u], fa);
+            }
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+                if (e >= left) { fq[e] = 0.f; fk[e] = 0.f; fa[e] = 1.f; continue; }
+                if (p.act) { fq[e] = silu_f(fq[e]); fk[e] = silu_f(fk[e]); }
+                fq[e] *= p.q_scale;
                 if (MODE == LA_DECAY_CHANNEL) {
-                    float z = ld_act(p.gate + t * p.gate_stride + (size_t)h * p.dk + c);
-                    if (p.gate_bias) z += p.gate_bias[(size_t)h * p.dk + c];
-                    av = expf(log_sigmoid(z) * p.inv_tau);
+                    float z = fa[e];
+                    if (p.gate_bias) z += p.gate_bias[(size_t)h * p.dk + c + e];
+                    fa[e] = expf(log_sigmoid(z) * p.inv_tau);
                 }
             }
-            sq[tt][c] = qv; sk[tt][c] = kv;
-            if (MODE == LA_DECAY_CHANNEL) sa[tt][c] = av;
-        }
-        for (int idx = threadIdx.x; idx < n * LA_COLS; idx += LA_THREADS) {
-            const int tt = idx / LA_COLS, c = idx - tt * LA_COLS;
-            float vv = 0.f;
-            if (col0 + c < p.dv) {
-                vv = ld_act(v + (size_t)(base + tt) * p.v_stride + col0 + c);
-                if (p.act) vv = silu_f(vv);
+            *reinterpret_cast<float4*>(&sq[tt][c]) = make_float4(fq[0], fq[1], fq[2], fq[3]);
+            *reinterpret_cast<float4*>(&sq[tt][c + 4]) = make_float4(fq[4], fq[5], fq[6], fq[7]);
+            *reinterpret_cast<float4*>(&sk[tt][c]) = make_float4(fk[0], fk[1], fk[2], fk[3]);
+            *reinterpret_cast<float4*>(&sk[tt][c + 4]) = make_float4(fk[4], fk[5], fk[6], fk[7]);
+            if (MODE == LA_DECAY_CHANNEL) {
+                *reinterpret_cast<float4*>(&sa[tt][c]) = make_float4(fa[0], fa[1], fa[2], fa[3]);
+                *reinterpret_cast<float4*>(&sa[tt][c + 4]) = make_float4(fa[4], fa[5], fa[6], fa[7]);
             }
-            sv[tt][c] = vv;
         }
+#pragma unroll
+        for (int u = 0; u < VPT; ++u) {
+            const int idx = threadIdx.x + u * LA_THREADS;
+            const int tt = idx / COLS, c = idx - tt * COLS;
+            if (idx < TS * COLS && tt < n) sv[tt][c] = p.act ? silu_f(rv[u]) : rv[u];
+        }
+    };
+
+    if (t0 < t1) fetch(t0, min(TS, t1 - t0));
+    for (int base = t0; base < t1; base += TS) {
+        const int n = min(TS, t1 - base);
+        __syncthreads();                                  // the stage before this one has been read
+        stage(n);
         __syncthreads();
+        if (base + TS < t1) fetch(base + TS, min(TS, t1 - base - TS));    // in flight while this stage is computed
+#pragma unroll 2
         for (int tt = 0; tt < n; ++tt) {
             const float vv = sv[tt][j];
             float acc[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
             for (int i = 0; i < NC; ++i) {
-                const int c = 4 * (kg + LA_KG * i);
+                const int c = 4 * (kg + KG * i);
                 const float4 kk = *reinterpret_cast<const float4*>(&sk[tt][c]);
                 const float4 qq = *reinterpret_cast<const float4*>(&sq[tt][c]);
                 float4 aa = make_float4(hd, hd, hd, hd);
@@ -136,8 +217,8 @@ linear_attention_kernel(LinAttnParams p) {
                 acc[3] = fmaf(st[i][3], qq.w, acc[3]);
             }
             float o = (acc[0] + acc[1]) + (acc[2] + acc[3]);
-            o += __shfl_xor_sync(0xffffffffu, o, 1);
-            o += __shfl_xor_sync(0xffffffffu, o, 2);
+#pragma unroll
+            for (int m = 1; m < KG; m <<= 1) o += __shfl_xor_sync(0xffffffffu, o, m);
             if (kg == 0 && col_ok) p.out[(size_t)(base + tt) * p.out_stride + (size_t)h * p.dv + col] = o;
         }
     }
@@ -146,7 +227,7 @@ linear_attention_kernel(LinAttnParams p) {
         for (int i = 0; i < NC; ++i)
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
-                const int c = 4 * (kg + LA_KG * i) + e;
+                const int c = 4 * (kg + KG * i) + e;
                 if (c < p.dk) S[(size_t)c * p.dv + col] = st[i][e];
             }
     }
@@ -183,6 +264,55 @@ __global__ void gated_norm_block_kernel(const float* __restrict__ o, const T* __
         float y = ld_act(orow + i) * scale * w[e % w_len];
         if (act != GATE_NONE) y *= gate_value(ld_act(gate + (size_t)t * gate_stride + e), act);
         out[(size_t)t * width + e] = from_f32<T>(y);
+    }
+}
+
+// The same with the group in registers: 256 threads, four columns a piece, up to four pieces a thread (groups of
+// up to 4,096 columns, a multiple of four, rows 16-byte aligned).  The gate's loads are issued before the sum.
+template <typename T>
+__global__ void __launch_bounds__(256)
+gated_norm_block_vec_kernel(const float* __restrict__ o, const T* __restrict__ gate, long long gate_stride,
+                            const float* __restrict__ w, int w_len, float eps, int act, float out_scale,
+                            T* __restrict__ out, int width, int group) {
+    __shared__ float scratch[32];
+    const int t = blockIdx.x, g = blockIdx.y;
+    pdl_wait();
+    const float* orow = o + (size_t)t * width + (size_t)g * group;
+    float4 v[4];
+    float gv[4][4];
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int c = (threadIdx.x + 256 * i) * 4;
+        if (c < group) {
+            v[i] = __ldcg(reinterpret_cast<const float4*>(orow + c));
+            if (act != GATE_NONE) {
+                const T* gp = gate + (size_t)t * gate_stride + (size_t)g * group + c;
+#pragma unroll
+                for (int e = 0; e < 4; ++e) gv[i][e] = ld_act(gp + e);
+            }
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+        if ((threadIdx.x + 256 * i) * 4 < group) {
+            ss = fmaf(v[i].x, v[i].x, ss); ss = fmaf(v[i].y, v[i].y, ss); ss = fmaf(v[i].z, v[i].z, ss); ss = fmaf(v[i].w, v[i].w, ss);
+        }
+    ss = block_sum(ss, scratch);
+    pdl_launch_dependents();
+    const float scale = rsqrtf(ss / (float)group + eps) * out_scale;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int c = (threadIdx.x + 256 * i) * 4;
+        if (c >= group) continue;
+        const int e0 = g * group + c;
+        const float x[4] = {v[i].x, v[i].y, v[i].z, v[i].w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            float y = x[e] * scale * w[(e0 + e) % w_len];
+            if (act != GATE_NONE) y *= gate_value(gv[i][e], act);
+            out[(size_t)t * width + e0 + e] = from_f32<T>(y);
+        }
     }
 }
 
@@ -233,10 +363,15 @@ extern "C" int tuff_linear_attention(const void* q, long long q_stride, const vo
     p.q_scale = q_scale; p.act = act; p.state = state; p.slot_of_row = slot_of_row; p.cu_q = cu_q;
     p.out = out; p.out_stride = out_stride; p.H = H; p.dk = dk; p.dv = dv; p.mode = mode;
     p.bounds = Bounds{(long long)n_rows, n_slots, status};
-    const dim3 grid(n_rows, H, ceil_div(dv, LA_COLS));
-#define LA_GO(T, NC, MODE) return launch_pdl(linear_attention_kernel<T, NC, MODE>, grid, dim3(LA_THREADS), 0, stream, p)
-#define LA_PICK(T, MODE) do { if (dk <= 32) LA_GO(T, 2, MODE); else if (dk <= 64) LA_GO(T, 4, MODE); \
-        else if (dk <= 128) LA_GO(T, 8, MODE); else LA_GO(T, 16, MODE); } while (0)
+    // Which thread owns which channels decides the order in which a token's products are added, so the choice
+    // between 32-column and 16-column tiles must not depend on the batch: it depends on the head's sizes only.
+    // 16-column tiles (8 threads a column) give twice the CTAs, each with half the work a token: what a prompt's
+    // few long rows need; a head of at most 32 key channels has too few for 8 threads.
+    const bool narrow = dk > 32;
+    const dim3 grid(n_rows, H, ceil_div(dv, narrow ? LA_THREADS / 8 : LA_THREADS / 4));
+#define LA_GO(T, NC, KG, MODE) return launch_pdl(linear_attention_kernel<T, NC, KG, MODE>, grid, dim3(LA_THREADS), 0, stream, p)
+#define LA_PICK(T, MODE) do { if (dk <= 32) LA_GO(T, 2, 4, MODE); else if (dk <= 64) LA_GO(T, 2, 8, MODE); \
+        else if (dk <= 128) LA_GO(T, 4, 8, MODE); else LA_GO(T, 8, 8, MODE); } while (0)
     if (dtype == TUFF_F32) { if (mode == LA_DECAY_HEAD) LA_PICK(float, LA_DECAY_HEAD); else LA_PICK(float, LA_DECAY_CHANNEL); }
     if (dtype == TUFF_BF16) { if (mode == LA_DECAY_HEAD) LA_PICK(bf16, LA_DECAY_HEAD); else LA_PICK(bf16, LA_DECAY_CHANNEL); }
 #undef LA_PICK
@@ -263,6 +398,9 @@ extern "C" int tuff_gated_group_norm(const float* o, const void* gate, long long
         return TUFF_E_DTYPE;
     }
     const dim3 grid(n_tokens, n_groups);
+    if (dtype == TUFF_BF16 && group % 4 == 0 && group <= 4096 && width % 4 == 0 && !((uintptr_t)o & 15))
+        return launch_pdl(gated_norm_block_vec_kernel<bf16>, grid, dim3(256), 0, stream, o, (const bf16*)gate, gate_stride, w, w_len,
+                          eps, act, out_scale, (bf16*)out, width, group);
 #define GN_GO(T) return launch_pdl(gated_norm_block_kernel<T>, grid, dim3(256), 0, stream, o, (const T*)gate, gate_stride, w, w_len, \
         eps, act, out_scale, (T*)out, width, group)
     if (dtype == TUFF_F32) GN_GO(float);

@@ -669,8 +669,13 @@ def attention_flash_supported(q: torch.Tensor, k_pages: torch.Tensor, H: int, G:
     return bool(lib.tuff_attention_flash_supported(c_int(H), c_int(G), c_int(hd), c_int(k_pages.shape[2])))
 
 
+def _attn_opts(chunk, sink, out_scale):
+    return (c_int(chunk or 0), c_int(0 if sink is None else 1), c_float(0.0 if sink is None else sink), c_float(out_scale))
+
+
 def attention_decode(q, k_pages, v_pages, block_table, positions, row_of_token, out, H, G, hd, scale,
-                     window: int = 0, max_seq_len: int | None = None) -> None:
+                     window: int = 0, max_seq_len: int | None = None, chunk: int = 0, sink: float | None = None,
+                     out_scale: float = 1.0) -> None:
     """Attention of a few query tokens over long cached contexts (bf16), the keys of each token cut
     into slices that run in parallel; `max_seq_len` (an upper bound on the contexts) sizes the cut."""
     n = q.shape[0]
@@ -684,12 +689,14 @@ def attention_decode(q, k_pages, v_pages, block_table, positions, row_of_token, 
                                      c_longlong(k_pages.shape[0]), _ptr(block_table), c_int(block_table.shape[1]),
                                      _ptr(positions), _ptr(row_of_token), _ptr(out), _ptr(ws), c_int(splits),
                                      _ptr(st["status"]), c_int(n), c_int(H), c_int(G), c_int(hd),
-                                     c_int(k_pages.shape[2]), c_float(scale), c_int(window), _stream()),
+                                     c_int(k_pages.shape[2]), c_float(scale), c_int(window),
+                                     *_attn_opts(chunk, sink, out_scale), _stream()),
            "attention_decode", kernels=2 if splits > 1 else 1)
 
 
 def attention_prefill(q, k_pages, v_pages, block_table, positions, row_of_token, cu_q, out, H, G, hd, scale,
-                      window: int = 0, n_tokens: int | None = None) -> None:
+                      window: int = 0, n_tokens: int | None = None, chunk: int = 0, sink: float | None = None,
+                      out_scale: float = 1.0) -> None:
     """Causal attention of prompt portions (bf16): blocks of query tokens against the cached keys."""
     n = q.shape[0] if n_tokens is None else n_tokens
     lib = load_library("attention_flash")
@@ -698,7 +705,8 @@ def attention_prefill(q, k_pages, v_pages, block_table, positions, row_of_token,
                                       c_longlong(k_pages.shape[0]), _ptr(block_table), c_int(block_table.shape[1]),
                                       _ptr(positions), _ptr(row_of_token), _ptr(cu_q), _ptr(out), _ptr(st["status"]),
                                       c_int(n), c_int(cu_q.numel() - 1), c_int(H), c_int(G), c_int(hd),
-                                      c_int(k_pages.shape[2]), c_float(scale), c_int(window), _stream()),
+                                      c_int(k_pages.shape[2]), c_float(scale), c_int(window),
+                                      *_attn_opts(chunk, sink, out_scale), _stream()),
            "attention_prefill")
 
 
@@ -716,7 +724,8 @@ def attention_prefill_tc_supported(q: torch.Tensor, k_pages: torch.Tensor, H: in
 
 
 def attention_prefill_tc(q, k_pages, v_pages, block_table, positions, cu_q, out, H, G, hd, scale,
-                         window: int = 0, n_tokens: int | None = None) -> None:
+                         window: int = 0, n_tokens: int | None = None, chunk: int = 0, sink: float | None = None,
+                         out_scale: float = 1.0) -> None:
     """Causal attention of prompt portions (bf16, head size 64) with tcgen05.mma: 128 query tokens
     of one head per CTA, scores and weighted values accumulated in tensor memory."""
     lib = load_library("attention_tc")
@@ -726,7 +735,8 @@ def attention_prefill_tc(q, k_pages, v_pages, block_table, positions, cu_q, out,
                                          _ptr(positions), _ptr(cu_q), _ptr(out), _ptr(st["status"]),
                                          c_int(q.shape[0] if n_tokens is None else n_tokens), c_int(cu_q.numel() - 1),
                                          c_int(H), c_int(G), c_int(hd),
-                                         c_int(k_pages.shape[2]), c_float(scale), c_int(window), _stream()),
+                                         c_int(k_pages.shape[2]), c_float(scale), c_int(window),
+                                         *_attn_opts(chunk, sink, out_scale), _stream()),
            "attention_prefill_tc")
 
 
@@ -745,40 +755,37 @@ def paged_attention(q, k_pages, v_pages, block_table, positions, row_of_token, o
         max_seq_len = ctx.max_seq_len if max_seq_len is None else max_seq_len
         single_prefix = ctx.single_prefix if single_prefix is None else single_prefix
     assert q.stride(1) == 1 and out.shape == (q.shape[0], H * hd) and q.dtype == k_pages.dtype == out.dtype
-    if chunk or sink is not None or out_scale != 1.0:
-        paged_attention_plain(q, k_pages, v_pages, block_table, positions, row_of_token, out, H, G, hd, scale, window,
-                              chunk=chunk, sink=sink, out_scale=out_scale)
-        return
+    opts = dict(chunk=chunk, sink=sink, out_scale=out_scale)
     n_rows = 0 if cu_q is None else cu_q.numel() - 1
     sp = int(single_prefix or 0)
     if (not all_single and cu_q is not None and 0 < sp < n_rows and attention_flash_supported(q, k_pages, H, G, hd)):
         # decoding rows first, then portions: tokens 0..sp-1 are the decoding rows' (one each)
         paged_attention(q[:sp], k_pages, v_pages, block_table[:sp], positions[:sp], row_of_token[:sp], out[:sp],
-                        H, G, hd, scale, window, cu_q=None, all_single=True, max_seq_len=max_seq_len, single_prefix=0)
+                        H, G, hd, scale, window, cu_q=None, all_single=True, max_seq_len=max_seq_len, single_prefix=0, **opts)
         # the portions keep their token numbering: q, positions and out stay whole, rows and their
         # tables are counted from the first portion
         _attention_portions(q, k_pages, v_pages, block_table[sp:], positions, row_of_token, cu_q[sp:], out,
-                            H, G, hd, scale, window, n_tokens=q.shape[0] - sp)
+                            H, G, hd, scale, window, n_tokens=q.shape[0] - sp, **opts)
         return
     if not all_single and cu_q is not None and attention_prefill_tc_supported(q, k_pages, H, G, hd):
-        _attention_portions(q, k_pages, v_pages, block_table, positions, row_of_token, cu_q, out, H, G, hd, scale, window)
+        _attention_portions(q, k_pages, v_pages, block_table, positions, row_of_token, cu_q, out, H, G, hd, scale, window, **opts)
         return
     if attention_flash_supported(q, k_pages, H, G, hd):
         _contig(out, "out"); _contig(k_pages, "k_pages"); _contig(v_pages, "v_pages"); _contig(block_table, "block_table")
         _i32(block_table, "block_table"); _i32(positions, "positions"); _i32(row_of_token, "row_of_token")
         if all_single or cu_q is None:
             attention_decode(q, k_pages, v_pages, block_table, positions, row_of_token, out, H, G, hd, scale, window,
-                             max_seq_len)
+                             max_seq_len, **opts)
         else:
             _i32(cu_q, "cu_q")
             attention_prefill(q, k_pages, v_pages, block_table, positions, row_of_token, cu_q, out, H, G, hd, scale,
-                              window)
+                              window, **opts)
         return
-    paged_attention_plain(q, k_pages, v_pages, block_table, positions, row_of_token, out, H, G, hd, scale, window)
+    paged_attention_plain(q, k_pages, v_pages, block_table, positions, row_of_token, out, H, G, hd, scale, window, **opts)
 
 
 def _attention_portions(q, k_pages, v_pages, block_table, positions, row_of_token, cu_q, out, H, G, hd, scale,
-                        window: int = 0, n_tokens: int | None = None) -> None:
+                        window: int = 0, n_tokens: int | None = None, **opts) -> None:
     """Rows of several tokens through the blocked kernels: tcgen05 where it applies, else mma.sync.
     `cu_q` holds token numbers into q/positions/out as they are; `block_table` starts at the first
     of these rows; `n_tokens`: how many tokens these rows bring (for sizing the launch)."""
@@ -786,11 +793,11 @@ def _attention_portions(q, k_pages, v_pages, block_table, positions, row_of_toke
     _i32(block_table, "block_table"); _i32(positions, "positions"); _i32(cu_q, "cu_q")
     if attention_prefill_tc_supported(q, k_pages, H, G, hd):
         attention_prefill_tc(q, k_pages, v_pages, block_table, positions, cu_q, out, H, G, hd, scale, window,
-                             n_tokens=n_tokens)
+                             n_tokens=n_tokens, **opts)
     else:
         _i32(row_of_token, "row_of_token")
         attention_prefill(q, k_pages, v_pages, block_table, positions, row_of_token, cu_q, out, H, G, hd, scale,
-                          window, n_tokens=n_tokens)
+                          window, n_tokens=n_tokens, **opts)
 
 
 # ------------------------------------------------------------ linear attention
