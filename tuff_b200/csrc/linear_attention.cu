@@ -42,6 +42,12 @@ struct LinAttnParams {
 };
 
 __device__ __forceinline__ float silu_f(float z) { return z / (1.f + expf(-z)); }
+// The bf16 engine's forms of the same functions in fp32 (ex2/lg2 approximations, relative error about 1e-6,
+// absolute error about 1e-7 on a decay's logarithm): an element costs a quarter of the exact forms' instructions.
+__device__ __forceinline__ float silu_fast(float z) { return __fdividef(z, 1.f + __expf(-z)); }
+__device__ __forceinline__ float decay_fast(float z, float inv_tau) {
+    return __expf((fminf(z, 0.f) - __logf(1.f + __expf(-fabsf(z)))) * inv_tau);
+}
 
 // log(sigmoid(z)) = -softplus(-z), computed without overflow for any z
 __device__ __forceinline__ float log_sigmoid(float z) {
@@ -154,9 +160,9 @@ linear_attention_kernel(LinAttnParams p) {
         for (int u = 0; u < UPT; ++u) {
             const int unit = threadIdx.x + u * LA_THREADS;
             const int tt = unit / (DKP / 8), c = (unit - tt * (DKP / 8)) * 8;
-            if (unit >= UNITS || tt >= n) continue;
+            if (unit >= UNITS) continue;
             float fq[8], fk[8], fa[8];
-            const int left = p.dk - c;
+            const int left = tt < n ? p.dk - c : 0;      // tokens beyond the row's end are neutral: k = q = 0, decay 1
             if (left > 0) {
                 unpack8(rq[u], fq); unpack8(rk[u], fk);
                 if (MODE == LA_DECAY_CHANNEL) unpack8(rg[u], fa);
@@ -164,12 +170,15 @@ linear_attention_kernel(LinAttnParams p) {
 #pragma unroll
             for (int e = 0; e < 8; ++e) {
                 if (e >= left) { fq[e] = 0.f; fk[e] = 0.f; fa[e] = 1.f; continue; }
-                if (p.act) { fq[e] = silu_f(fq[e]); fk[e] = silu_f(fk[e]); }
+                if (p.act) {
+                    if (sizeof(T) == 2) { fq[e] = silu_fast(fq[e]); fk[e] = silu_fast(fk[e]); }
+                    else { fq[e] = silu_f(fq[e]); fk[e] = silu_f(fk[e]); }
+                }
                 fq[e] *= p.q_scale;
                 if (MODE == LA_DECAY_CHANNEL) {
                     float z = fa[e];
                     if (p.gate_bias) z += p.gate_bias[(size_t)h * p.dk + c + e];
-                    fa[e] = expf(log_sigmoid(z) * p.inv_tau);
+                    fa[e] = sizeof(T) == 2 ? decay_fast(z, p.inv_tau) : expf(log_sigmoid(z) * p.inv_tau);
                 }
             }
             *reinterpret_cast<float4*>(&sq[tt][c]) = make_float4(fq[0], fq[1], fq[2], fq[3]);
@@ -185,7 +194,7 @@ linear_attention_kernel(LinAttnParams p) {
         for (int u = 0; u < VPT; ++u) {
             const int idx = threadIdx.x + u * LA_THREADS;
             const int tt = idx / COLS, c = idx - tt * COLS;
-            if (idx < TS * COLS && tt < n) sv[tt][c] = p.act ? silu_f(rv[u]) : rv[u];
+            if (idx < TS * COLS) sv[tt][c] = tt >= n ? 0.f : !p.act ? rv[u] : sizeof(T) == 2 ? silu_fast(rv[u]) : silu_f(rv[u]);
         }
     };
 
@@ -196,30 +205,41 @@ linear_attention_kernel(LinAttnParams p) {
         stage(n);
         __syncthreads();
         if (base + TS < t1) fetch(base + TS, min(TS, t1 - base - TS));    // in flight while this stage is computed
-#pragma unroll 2
-        for (int tt = 0; tt < n; ++tt) {
-            const float vv = sv[tt][j];
-            float acc[4] = {0.f, 0.f, 0.f, 0.f};
+        // four tokens at a time: their loads, their sums and the exchange between the threads of a column overlap
+        for (int tb = 0; tb < n; tb += 4) {
+            float part[4];
 #pragma unroll
-            for (int i = 0; i < NC; ++i) {
-                const int c = 4 * (kg + KG * i);
-                const float4 kk = *reinterpret_cast<const float4*>(&sk[tt][c]);
-                const float4 qq = *reinterpret_cast<const float4*>(&sq[tt][c]);
-                float4 aa = make_float4(hd, hd, hd, hd);
-                if (MODE == LA_DECAY_CHANNEL) aa = *reinterpret_cast<const float4*>(&sa[tt][c]);
-                st[i][0] = fmaf(aa.x, st[i][0], kk.x * vv);
-                st[i][1] = fmaf(aa.y, st[i][1], kk.y * vv);
-                st[i][2] = fmaf(aa.z, st[i][2], kk.z * vv);
-                st[i][3] = fmaf(aa.w, st[i][3], kk.w * vv);
-                acc[0] = fmaf(st[i][0], qq.x, acc[0]);
-                acc[1] = fmaf(st[i][1], qq.y, acc[1]);
-                acc[2] = fmaf(st[i][2], qq.z, acc[2]);
-                acc[3] = fmaf(st[i][3], qq.w, acc[3]);
+            for (int u = 0; u < 4; ++u) {
+                const int tt = tb + u;
+                const float vv = sv[tt][j];
+                const float hdu = tt < n ? hd : 1.f;      // a token beyond the row's end leaves the state as it is
+                float acc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+                for (int i = 0; i < NC; ++i) {
+                    const int c = 4 * (kg + KG * i);
+                    const float4 kk = *reinterpret_cast<const float4*>(&sk[tt][c]);
+                    const float4 qq = *reinterpret_cast<const float4*>(&sq[tt][c]);
+                    float4 aa = make_float4(hdu, hdu, hdu, hdu);
+                    if (MODE == LA_DECAY_CHANNEL) aa = *reinterpret_cast<const float4*>(&sa[tt][c]);
+                    st[i][0] = fmaf(aa.x, st[i][0], kk.x * vv);
+                    st[i][1] = fmaf(aa.y, st[i][1], kk.y * vv);
+                    st[i][2] = fmaf(aa.z, st[i][2], kk.z * vv);
+                    st[i][3] = fmaf(aa.w, st[i][3], kk.w * vv);
+                    acc[0] = fmaf(st[i][0], qq.x, acc[0]);
+                    acc[1] = fmaf(st[i][1], qq.y, acc[1]);
+                    acc[2] = fmaf(st[i][2], qq.z, acc[2]);
+                    acc[3] = fmaf(st[i][3], qq.w, acc[3]);
+                }
+                part[u] = (acc[0] + acc[1]) + (acc[2] + acc[3]);
             }
-            float o = (acc[0] + acc[1]) + (acc[2] + acc[3]);
 #pragma unroll
-            for (int m = 1; m < KG; m <<= 1) o += __shfl_xor_sync(0xffffffffu, o, m);
-            if (kg == 0 && col_ok) p.out[(size_t)(base + tt) * p.out_stride + (size_t)h * p.dv + col] = o;
+            for (int m = 1; m < KG; m <<= 1)
+#pragma unroll
+                for (int u = 0; u < 4; ++u) part[u] += __shfl_xor_sync(0xffffffffu, part[u], m);
+#pragma unroll
+            for (int u = 0; u < 4; ++u)       // every thread of the column has the sums: thread u writes token u
+                if (kg == u && col_ok && tb + u < n)
+                    p.out[(size_t)(base + tb + u) * p.out_stride + (size_t)h * p.dv + col] = part[u];
         }
     }
     if (col_ok) {
