@@ -32,7 +32,7 @@ def _ids(text: str) -> List[int]:
 
 
 def build_parser() -> argparse.ArgumentParser:
-    ap = argparse.ArgumentParser(prog="tuff", description="LFM2/LFM2.5 dense inference on one B200")
+    ap = argparse.ArgumentParser(prog="tuff", description="LFM2/LFM2.5 and Koridra inference on one B200")
     ap.add_argument("--model", help="model folder (config.json + model.safetensors)")
     ap.add_argument("--random", metavar="CONFIG.json", help="make a random-weights model from this config.json")
     ap.add_argument("--weight-seed", type=int, default=0)

@@ -60,15 +60,28 @@ template <typename T> struct Raw8;
 template <> struct Raw8<bf16> { uint4 v; };
 template <> struct Raw8<float> { float4 a, b; };
 
+// The loads of a stage are issued where they stand (volatile): moved down to their first use they would
+// no longer overlap the stage that is computed in between.
+__device__ __forceinline__ uint4 ld_early_u4(const void* p) {
+    uint4 v;
+    asm volatile("ld.global.cg.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+    return v;
+}
+
 __device__ __forceinline__ void load8(Raw8<bf16>& r, const bf16* p, bool vec, int n_valid) {
-    if (vec) { r.v = ld_act_u4(p); return; }
+    if (vec) { r.v = ld_early_u4(p); return; }
     unsigned short h[8];
 #pragma unroll
     for (int e = 0; e < 8; ++e) h[e] = e < n_valid ? __ldcg(reinterpret_cast<const unsigned short*>(p) + e) : (unsigned short)0;
     r.v = make_uint4(h[0] | (uint32_t)h[1] << 16, h[2] | (uint32_t)h[3] << 16, h[4] | (uint32_t)h[5] << 16, h[6] | (uint32_t)h[7] << 16);
 }
 __device__ __forceinline__ void load8(Raw8<float>& r, const float* p, bool vec, int n_valid) {
-    if (vec) { r.a = __ldcg(reinterpret_cast<const float4*>(p)); r.b = __ldcg(reinterpret_cast<const float4*>(p) + 1); return; }
+    if (vec) {
+        const uint4 a = ld_early_u4(p), b = ld_early_u4(p + 4);
+        r.a = make_float4(__uint_as_float(a.x), __uint_as_float(a.y), __uint_as_float(a.z), __uint_as_float(a.w));
+        r.b = make_float4(__uint_as_float(b.x), __uint_as_float(b.y), __uint_as_float(b.z), __uint_as_float(b.w));
+        return;
+    }
     float f[8];
 #pragma unroll
     for (int e = 0; e < 8; ++e) f[e] = e < n_valid ? __ldcg(p + e) : 0.f;
