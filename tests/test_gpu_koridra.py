@@ -21,8 +21,9 @@ pytestmark = pytest.mark.gpu
 
 # Root mean square of the difference of a logits row (mean taken off) over that of the row itself.
 ROW_TOL = {"float32": 2e-4, "bfloat16": 6e-2}
-LENGTHS = {"kor_a": (70, 45, 97, 130, 66), "kor_b": (83, 40, 129, 65, 100), "kor_c": (150, 64, 37, 200, 129)}
-PAGE = {"kor_a": 16, "kor_b": 4, "kor_c": 64}
+LENGTHS = {"kor_a": (70, 45, 97, 130, 66), "kor_b": (83, 40, 129, 65, 100), "kor_c": (150, 64, 37, 200, 129),
+           "kor_d": (120, 51, 33, 160, 101)}
+PAGE = {"kor_a": 16, "kor_b": 4, "kor_c": 64, "kor_d": 16}
 
 
 def row_error(got, ref):
@@ -200,7 +201,7 @@ def test_lightning_attention_part(dtype, H, dk, dv):
 def test_gated_linear_attention_part(dtype, H, dk, dv, tau, rank):
     from tuff_b200.parts import MIXERS, PartSpec
     rng = np.random.default_rng(H + dk)
-    d, eps = 64, 1e-6
+    d, eps = 64, 0.02          # an eps of the size of the read-out's mean square: the scale of q shows through the norm
     m = dict(heads=H, dim=dk, vdim=dv, tau=tau)
     part = MIXERS.build(PartSpec("gated_linear_attention", dict(d_model=d, norm_eps=eps, gate_rank=rank, out_scale=1.3, **m)))
     w = bind_random(part, dtype, rng, std=0.3)
@@ -323,6 +324,51 @@ def test_one_key_stands_out_at_the_edges_of_a_chunk(mode, page):
             assert np.abs(got[last_in + 1, 0] - v[key_at]).max() > 0.1                # and not one place later
         if key_at > 0:
             assert np.abs(got[key_at - 1, 0] - v[key_at]).max() > 0.1                 # nor before it exists
+
+
+@pytest.mark.parametrize("hd,page", [(64, 16), (64, 64), (128, 8), (128, 64)])
+def test_chunk_edges_and_sink_in_the_tensor_core_kernels(hd, page):
+    """The same question put to the bf16 kernels (tcgen05 for portions of head size 64, TMA + mma.sync for head size
+    128 and for single tokens, sliced over the keys): portions of 128 and of 7 tokens and tokens one by one."""
+    from tuff_b200.kernels import ops
+    H, G, T = 4, 2, 300
+    rng = np.random.default_rng(hd + page)
+    bf = torch.bfloat16
+    for chunk, key_at in ((96, 96), (96, 191), (250, 5), (0, 2), (64, 63)):
+        k = f64(dev(0.1 * rng.normal(size=(T, G * hd)), bf)); v = f64(dev(rng.normal(size=(T, G * hd)), bf))
+        q = f64(dev(0.1 * rng.normal(size=(T, H * hd)), bf))
+        k[key_at, :hd] = 0.0; k[key_at, 0] = 30.0
+        q[:, 0] = 1.0; q[:, hd] = 1.0                        # the two heads of group 0 ask for it
+        n_pages = (T + page - 1) // page
+        kp = torch.zeros(n_pages + 1, G, page, hd, device="cuda", dtype=bf); vp = torch.zeros_like(kp)
+        table = torch.arange(n_pages, dtype=torch.int32, device="cuda").flip(0).reshape(1, -1).contiguous()
+        pages = table[0].long()
+        for t in range(T):
+            kp[pages[t // page], :, t % page] = dev(k[t], bf).view(G, hd); vp[pages[t // page], :, t % page] = dev(v[t], bf).view(G, hd)
+        positions = torch.arange(T, dtype=torch.int32, device="cuda")
+        rows = torch.zeros(T, dtype=torch.int32, device="cuda")
+        ok = plain.chunk_mask(T, chunk)
+        ref = np.zeros((T, H, hd))
+        for a in range(H):
+            g = a // (H // G)
+            ref[:, a] = 0.5 * plain.sink_softmax(q[:, a * hd:(a + 1) * hd] @ k[:, g * hd:(g + 1) * hd].T, ok) @ v[:, g * hd:(g + 1) * hd]
+        qd = dev(q, bf)
+        for cuts in ((128, 7, 1, 1, 100, 63), (1,) * 40 + (260,)):
+            out = torch.zeros(T, H * hd, device="cuda", dtype=bf)
+            p = 0
+            for n in cuts:
+                n = min(n, T - p)
+                single = n == 1
+                ops.paged_attention(qd[p:p + n], kp, vp, table, positions[p:p + n], rows[:n], out[p:p + n], H, G, hd, 1.0,
+                                    chunk=chunk, sink=0.0, out_scale=0.5, all_single=single, max_seq_len=T,
+                                    cu_q=None if single else torch.tensor([0, n], dtype=torch.int32, device="cuda"), single_prefix=0)
+                p += n
+            got = f64(out).reshape(T, H, hd)
+            assert np.abs(got - ref).max() <= 2e-2, (chunk, key_at, cuts[:3], np.abs(got - ref).max())
+        last_in = T - 1 if not chunk else min(T - 1, (key_at // chunk + 1) * chunk - 1)
+        assert np.abs(got[last_in, 0] - 0.5 * v[key_at, :hd]).max() < 2e-2
+        if last_in + 1 < T:
+            assert np.abs(got[last_in + 1, 0] - 0.5 * v[key_at, :hd]).max() > 0.05
 
 
 def test_the_sink_takes_its_share():

@@ -1,5 +1,5 @@
 """Small Koridra configurations for the tests, and model folders with weights large enough that every
-mechanism shows in the logits.  The three differ from one another in every size and option: layer order
+mechanism shows in the logits.  They differ from one another in every size and option: layer order
 (a parallel layer first / two of them / none but the last), layers without feed-forward, query and value
 sizes that differ, key/value groups, rotated spans (half, whole, none), YaRN on and off, chunks that are
 no multiple of a page, gate widths that the tensor-core product refuses (5), tau down to 1, alpha down
@@ -52,7 +52,18 @@ KOR_C = dict(
                   dict(heads=2, dim=64, vdim=64, tau=16.0, gate_rank=24), 0.6, 1.1, 256),
     ])
 
-CONFIGS = {"kor_a": (KOR_A, 11), "kor_b": (KOR_B, 12), "kor_c": (KOR_C, 13)}
+# a width and a vocabulary that are no multiple of 8 (no tensor-core product takes them), head size 128 in the softmax
+# branch (the TMA-fed attention kernels' other size), a chunk that is no multiple of anything, a gate width of 6
+KOR_D = dict(
+    architecture="Koridra", vocab=211, width=100, max_positions=256, norm=dict(eps=1e-5), postln_alpha=2.5,
+    layers=[
+        _parallel(dict(heads=2, kv_heads=1, dim=128, vdim=128, scale=0.09, mask=dict(size=50),
+                       rot=dict(dims=64, base=1e4, scaling=dict(factor=2.0, original=32, fast=8.0, slow=1.0))),
+                  dict(heads=2, dim=20, vdim=12, tau=2.0, gate_rank=6), 0.8, 0.9, 72),
+        _lightning(2, 24, 36, [0.9, 0.99], 72),
+    ])
+
+CONFIGS = {"kor_a": (KOR_A, 11), "kor_b": (KOR_B, 12), "kor_c": (KOR_C, 13), "kor_d": (KOR_D, 14)}
 
 
 def make_folder(tmp_path, name, gain=1.0):
