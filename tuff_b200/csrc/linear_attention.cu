@@ -22,6 +22,8 @@
 
 namespace {
 constexpr int LA_THREADS = 128;         // 4 warps: value columns x threads that share a column
+constexpr int LA_GROUP = 4;             // tokens whose sums and exchanges are in flight together
+template <int N> struct GroupOf { static constexpr int value = N; };
 
 enum { LA_DECAY_HEAD = 0, LA_DECAY_CHANNEL = 1 };
 
@@ -96,6 +98,12 @@ __device__ __forceinline__ void unpack8(const Raw8<float>& r, float (&f)[8]) {
     f[0] = r.a.x; f[1] = r.a.y; f[2] = r.a.z; f[3] = r.a.w; f[4] = r.b.x; f[5] = r.b.y; f[6] = r.b.z; f[7] = r.b.w;
 }
 
+// One element as it lies in memory (converted where it is used, not where it is loaded).
+__device__ __forceinline__ unsigned short ld_raw(const bf16* p) { return __ldcg(reinterpret_cast<const unsigned short*>(p)); }
+__device__ __forceinline__ float ld_raw(const float* p) { return __ldcg(p); }
+__device__ __forceinline__ float raw_f32(unsigned short v) { return __uint_as_float((uint32_t)v << 16); }
+__device__ __forceinline__ float raw_f32(float v) { return v; }
+
 // NC: groups of four key channels a thread owns; KG: threads that share a value column (dk <= 4 * KG * NC).
 // A CTA covers 128 / KG value columns: KG = 4 for batches that fill the GPU with 32-column tiles, KG = 8 (16
 // columns, twice the CTAs, half the work a token costs a thread) for the few long rows of a prompt.
@@ -145,7 +153,8 @@ linear_attention_kernel(LinAttnParams p) {
 
     Raw8<T> rq[UPT], rk[UPT];
     Raw8<float> rg[MODE == LA_DECAY_CHANNEL ? UPT : 1];
-    float rv[VPT];
+    decltype(ld_raw((const T*)nullptr)) rv[VPT];
+    bool rv_ok[VPT];
     // the loads of the stage that begins at token `base` (n tokens), into registers
     auto fetch = [&](int base, int n) {
 #pragma unroll
@@ -164,7 +173,8 @@ linear_attention_kernel(LinAttnParams p) {
         for (int u = 0; u < VPT; ++u) {
             const int idx = threadIdx.x + u * LA_THREADS;
             const int tt = idx / COLS, c = idx - tt * COLS;
-            rv[u] = (idx < TS * COLS && tt < n && col0 + c < p.dv) ? ld_act(v + (size_t)(base + tt) * p.v_stride + col0 + c) : 0.f;
+            rv_ok[u] = idx < TS * COLS && tt < n && col0 + c < p.dv;
+            if (rv_ok[u]) rv[u] = ld_raw(v + (size_t)(base + tt) * p.v_stride + col0 + c);
         }
     };
     // activation, scale and decay once per element, into shared memory
@@ -207,7 +217,8 @@ linear_attention_kernel(LinAttnParams p) {
         for (int u = 0; u < VPT; ++u) {
             const int idx = threadIdx.x + u * LA_THREADS;
             const int tt = idx / COLS, c = idx - tt * COLS;
-            if (idx < TS * COLS) sv[tt][c] = tt >= n ? 0.f : !p.act ? rv[u] : sizeof(T) == 2 ? silu_fast(rv[u]) : silu_f(rv[u]);
+            const float x = rv_ok[u] ? raw_f32(rv[u]) : 0.f;
+            if (idx < TS * COLS) sv[tt][c] = !p.act ? x : sizeof(T) == 2 ? silu_fast(x) : silu_f(x);
         }
     };
 
@@ -218,21 +229,22 @@ linear_attention_kernel(LinAttnParams p) {
         stage(n);
         __syncthreads();
         if (base + TS < t1) fetch(base + TS, min(TS, t1 - base - TS));    // in flight while this stage is computed
-        // four tokens at a time: their loads, their sums and the exchange between the threads of a column overlap
-        for (int tb = 0; tb < n; tb += 4) {
-            float part[4];
+        // four tokens at a time (their shared-memory reads, their sums and the exchange between the threads of a
+        // column overlap), then what is left of the row one token at a time; a token's arithmetic is the same in both
+        auto tokens = [&](int tb, auto group) {
+            constexpr int GR = decltype(group)::value;
+            float part[GR];
 #pragma unroll
-            for (int u = 0; u < 4; ++u) {
+            for (int u = 0; u < GR; ++u) {
                 const int tt = tb + u;
                 const float vv = sv[tt][j];
-                const float hdu = tt < n ? hd : 1.f;      // a token beyond the row's end leaves the state as it is
                 float acc[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
                 for (int i = 0; i < NC; ++i) {
                     const int c = 4 * (kg + KG * i);
                     const float4 kk = *reinterpret_cast<const float4*>(&sk[tt][c]);
                     const float4 qq = *reinterpret_cast<const float4*>(&sq[tt][c]);
-                    float4 aa = make_float4(hdu, hdu, hdu, hdu);
+                    float4 aa = make_float4(hd, hd, hd, hd);
                     if (MODE == LA_DECAY_CHANNEL) aa = *reinterpret_cast<const float4*>(&sa[tt][c]);
                     st[i][0] = fmaf(aa.x, st[i][0], kk.x * vv);
                     st[i][1] = fmaf(aa.y, st[i][1], kk.y * vv);
@@ -248,12 +260,15 @@ linear_attention_kernel(LinAttnParams p) {
 #pragma unroll
             for (int m = 1; m < KG; m <<= 1)
 #pragma unroll
-                for (int u = 0; u < 4; ++u) part[u] += __shfl_xor_sync(0xffffffffu, part[u], m);
+                for (int u = 0; u < GR; ++u) part[u] += __shfl_xor_sync(0xffffffffu, part[u], m);
 #pragma unroll
-            for (int u = 0; u < 4; ++u)       // every thread of the column has the sums: thread u writes token u
-                if (kg == u && col_ok && tb + u < n)
+            for (int u = 0; u < GR; ++u)       // every thread of the column has the sums: thread u writes token u
+                if (kg == u && col_ok)
                     p.out[(size_t)(base + tb + u) * p.out_stride + (size_t)h * p.dv + col] = part[u];
-        }
+        };
+        int tb = 0;
+        for (; tb + LA_GROUP <= n; tb += LA_GROUP) tokens(tb, GroupOf<LA_GROUP>{});
+        for (; tb < n; ++tb) tokens(tb, GroupOf<1>{});
     }
     if (col_ok) {
 #pragma unroll
