@@ -227,7 +227,7 @@ def test_a_far_token_stays_in_the_state():
     decay = np.array([0.99, 0.5])
     ref = plain.decaying_state_scan(q.reshape(T, H, dk), k.reshape(T, H, dk), v.reshape(T, H, dv), decay[None, :, None])
     assert abs(ref[T - 1, 0, 3] - 100.0 * 4.0 * 0.99 ** (T - 8)) < 0.05 * abs(ref[T - 1, 0, 3])     # the test shows what it says
-    state = torch.zeros(3, H, dk, dv, device="cuda")
+    state = torch.zeros(3, H, dv, dk, device="cuda")
     out = torch.empty(T, H * dv, device="cuda")
     cuts, p = [5, 2, 1, 33, 64, 2, 100, 17, 1, 95], 0
     for n in cuts:

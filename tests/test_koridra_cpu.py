@@ -55,8 +55,8 @@ def test_model_description_and_tensor_names():
     assert "l2.norm2" not in exp and "l2.mlp.gate" not in exp and "l0.mix.left.v" not in exp
     assert exp["pos"].shape == (400, 80) and exp["head"].shape == (301, 80)
     needs = model.storage_needs()
-    assert needs[0] == CompositeNeed((PagedKVNeed(2, 32, chunk=24), StateNeed((2, 24, 40))))
-    assert needs[1] == StateNeed((3, 16, 40)) and model.replayable
+    assert needs[0] == CompositeNeed((PagedKVNeed(2, 32, chunk=24), StateNeed((2, 40, 24))))
+    assert needs[1] == StateNeed((3, 40, 16)) and model.replayable
 
 
 def test_a_size_that_only_the_checkpoint_gives(tmp_path):

@@ -1,7 +1,7 @@
 // Linear attention with a decaying matrix state per head, and the gated norm that follows it.
 //
 //   tuff_linear_attention   per (request, head): S_t = diag(a_t) S_(t-1) + k_t v_t^T,  o_t = S_t^T q_t
-//                           S is [dk, dv] in fp32 in the request's state slot; a_t is either one factor
+//                           S is [dk, dv] in fp32, kept transposed ([dv, dk]) in the request's state slot; a_t is either one factor
 //                           per head (a constant of the layer) or a factor per key channel and token,
 //                           a = sigmoid(z)^(1/tau) with z = gate + bias taken per token
 //   tuff_gated_group_norm   y = rmsnorm_group(o) * weight * act(gate) * out_scale, groups of any width
@@ -11,17 +11,19 @@
 // recurrence runs on FFMA.  q, k and v come from the projections in the activation dtype; an
 // activation (silu) and a scale of q are applied when a token's vectors are staged.
 //
-// One CTA owns (batch row, head, 16 or 32 value columns) and walks the row's tokens in order; a thread owns
-// one value column and every eighth (fourth) group of four key channels, so a token costs it dk/8 (dk/4) state
-// elements in registers and three (two) shuffles.  Tokens are staged through shared memory 16 at a time
-// (activation, decay and scale computed once per element there); the next stage's loads are issued into
-// registers before the current stage is computed.  The order of all sums depends on the sizes only: a request's
-// state and outputs are the same bits however its tokens were cut into steps or batched.
+// One CTA of 8 warps owns (batch row, head, 16 value columns; 32 for heads of at most 32 key channels) and walks
+// the row's tokens in order; 16 (8) threads share a column, each with every 16th (8th) group of four key channels
+// of that column's state in registers, so a token costs a thread dk/16 multiply-adds into the state, as many into
+// the read-out, and four (three) shuffle steps per four tokens.  The state lies [head][value column][key channel]
+// in its slot, so a thread's four channels are one 16-byte access and a warp's accesses are whole lines.  Tokens are
+// staged through shared memory 16 at a time (activation, decay and scale computed once per element there); the
+// next stage's loads are issued into registers before the current stage is computed.  The order of all sums depends
+// on the sizes only: a request's state and outputs are the same bits however its tokens were cut into steps or batched.
 #include "common.cuh"
 #include "index.cuh"
 
 namespace {
-constexpr int LA_THREADS = 128;         // 4 warps: value columns x threads that share a column
+constexpr int LA_THREADS = 256;         // 8 warps: value columns x threads that share a column
 constexpr int LA_GROUP = 4;             // tokens whose sums and exchanges are in flight together
 template <int N> struct GroupOf { static constexpr int value = N; };
 
@@ -36,7 +38,7 @@ struct LinAttnParams {
     float inv_tau;
     float q_scale;
     int act;                                              // 1: silu on q, k and v
-    float* state;                                         // [slots, H, dk, dv]
+    float* state;                                         // [slots, H, dv, dk]
     const int* slot_of_row; const int* cu_q;
     float* out; long long out_stride;                     // fp32 [T, H*dv]
     int H, dk, dv, mode;
@@ -105,8 +107,7 @@ __device__ __forceinline__ float raw_f32(unsigned short v) { return __uint_as_fl
 __device__ __forceinline__ float raw_f32(float v) { return v; }
 
 // NC: groups of four key channels a thread owns; KG: threads that share a value column (dk <= 4 * KG * NC).
-// A CTA covers 128 / KG value columns: KG = 4 for batches that fill the GPU with 32-column tiles, KG = 8 (16
-// columns, twice the CTAs, half the work a token costs a thread) for the few long rows of a prompt.
+// A CTA covers 256 / KG value columns.
 template <typename T, int NC, int KG, int MODE>
 __global__ void __launch_bounds__(LA_THREADS)
 linear_attention_kernel(LinAttnParams p) {
@@ -141,14 +142,20 @@ linear_attention_kernel(LinAttnParams p) {
                         !((uintptr_t)q & 15) && !((uintptr_t)k & 15);
     const bool vec_g = MODE == LA_DECAY_CHANNEL && p.dk % 8 == 0 && p.gate_stride % 4 == 0 && !((uintptr_t)gate & 15);
 
+    float* Scol = S + (size_t)col * p.dk;                  // this column's dk channels, contiguous
+    const bool vec_s = p.dk % 4 == 0;                      // slots and heads then start on 16-byte boundaries
     float st[NC][4];
 #pragma unroll
-    for (int i = 0; i < NC; ++i)
+    for (int i = 0; i < NC; ++i) {
+        const int c = 4 * (kg + KG * i);
+        if (col_ok && vec_s && c < p.dk) {
+            const float4 v4 = *reinterpret_cast<const float4*>(Scol + c);
+            st[i][0] = v4.x; st[i][1] = v4.y; st[i][2] = v4.z; st[i][3] = v4.w;
+        } else {
 #pragma unroll
-        for (int e = 0; e < 4; ++e) {
-            const int c = 4 * (kg + KG * i) + e;
-            st[i][e] = (col_ok && c < p.dk) ? S[(size_t)c * p.dv + col] : 0.f;
+            for (int e = 0; e < 4; ++e) st[i][e] = (col_ok && c + e < p.dk) ? Scol[c + e] : 0.f;
         }
+    }
     const float hd = MODE == LA_DECAY_HEAD ? p.head_decay[h] : 1.f;
 
     Raw8<T> rq[UPT], rk[UPT];
@@ -272,12 +279,16 @@ linear_attention_kernel(LinAttnParams p) {
     }
     if (col_ok) {
 #pragma unroll
-        for (int i = 0; i < NC; ++i)
+        for (int i = 0; i < NC; ++i) {
+            const int c = 4 * (kg + KG * i);
+            if (vec_s && c < p.dk) {
+                *reinterpret_cast<float4*>(Scol + c) = make_float4(st[i][0], st[i][1], st[i][2], st[i][3]);
+            } else {
 #pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                const int c = 4 * (kg + KG * i) + e;
-                if (c < p.dk) S[(size_t)c * p.dv + col] = st[i][e];
+                for (int e = 0; e < 4; ++e)
+                    if (c + e < p.dk) Scol[c + e] = st[i][e];
             }
+        }
     }
 }
 
@@ -395,7 +406,8 @@ gated_norm_warp_kernel(const float* __restrict__ o, const T* __restrict__ gate, 
 }
 }  // namespace
 
-// q, k [n_tokens, >= H*dk], v [n_tokens, >= H*dv] in `dtype` with their row strides; out fp32.
+// q, k [n_tokens, >= H*dk], v [n_tokens, >= H*dv] in `dtype` with their row strides; out fp32;
+// state fp32 [n_slots, H, dv, dk].
 // mode 0: head_decay[H]; mode 1: gate fp32 [n_tokens, H*dk] (+ gate_bias), a = sigmoid(z)^(inv_tau).
 extern "C" int tuff_linear_attention(const void* q, long long q_stride, const void* k, long long k_stride,
                                      const void* v, long long v_stride, int dtype, int mode, const float* head_decay,
@@ -412,14 +424,12 @@ extern "C" int tuff_linear_attention(const void* q, long long q_stride, const vo
     p.out = out; p.out_stride = out_stride; p.H = H; p.dk = dk; p.dv = dv; p.mode = mode;
     p.bounds = Bounds{(long long)n_rows, n_slots, status};
     // Which thread owns which channels decides the order in which a token's products are added, so the choice
-    // between 32-column and 16-column tiles must not depend on the batch: it depends on the head's sizes only.
-    // 16-column tiles (8 threads a column) give twice the CTAs, each with half the work a token: what a prompt's
-    // few long rows need; a head of at most 32 key channels has too few for 8 threads.
-    const bool narrow = dk > 32;
-    const dim3 grid(n_rows, H, ceil_div(dv, narrow ? LA_THREADS / 8 : LA_THREADS / 4));
+    // of tile must not depend on the batch: it depends on the head's key size only.
+    const int cols = dk <= 32 ? LA_THREADS / 8 : LA_THREADS / 16;
+    const dim3 grid(n_rows, H, ceil_div(dv, cols));
 #define LA_GO(T, NC, KG, MODE) return launch_pdl(linear_attention_kernel<T, NC, KG, MODE>, grid, dim3(LA_THREADS), 0, stream, p)
-#define LA_PICK(T, MODE) do { if (dk <= 32) LA_GO(T, 2, 4, MODE); else if (dk <= 64) LA_GO(T, 2, 8, MODE); \
-        else if (dk <= 128) LA_GO(T, 4, 8, MODE); else LA_GO(T, 8, 8, MODE); } while (0)
+#define LA_PICK(T, MODE) do { if (dk <= 32) LA_GO(T, 1, 8, MODE); else if (dk <= 64) LA_GO(T, 1, 16, MODE); \
+        else if (dk <= 128) LA_GO(T, 2, 16, MODE); else LA_GO(T, 4, 16, MODE); } while (0)
     if (dtype == TUFF_F32) { if (mode == LA_DECAY_HEAD) LA_PICK(float, LA_DECAY_HEAD); else LA_PICK(float, LA_DECAY_CHANNEL); }
     if (dtype == TUFF_BF16) { if (mode == LA_DECAY_HEAD) LA_PICK(bf16, LA_DECAY_HEAD); else LA_PICK(bf16, LA_DECAY_CHANNEL); }
 #undef LA_PICK

@@ -806,7 +806,7 @@ def linear_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, state: t
                      gate: torch.Tensor | None = None, gate_bias: torch.Tensor | None = None, tau: float = 1.0,
                      q_scale: float = 1.0, silu: bool = False) -> None:
     """Per request and head S_t = diag(a_t) S_(t-1) + k_t v_t^T, o_t = S_t^T q_t, over a batch of portions;
-    the state [slots, H, dk, dv] (fp32) of each row's slot is continued and left updated.
+    the state (fp32, kept transposed: [slots, H, dv, dk]) of each row's slot is continued and left updated.
     q, k [n, >= H*dk] and v [n, >= H*dv] are views with a row stride; out fp32 [n, H*dv].
     Decay: `head_decay` fp32 [H] (one factor per head), or `gate` fp32 [n, H*dk] (+ `gate_bias` [H*dk]) with
     a = sigmoid(gate + bias)^(1/tau) per key channel and token.  `silu`: applied to q, k and v; q * q_scale."""
@@ -814,7 +814,7 @@ def linear_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, state: t
     n = out.shape[0]
     assert (head_decay is None) != (gate is None)
     assert q.dtype == k.dtype == v.dtype and out.dtype == torch.float32 and state.dtype == torch.float32
-    assert q.shape[0] == k.shape[0] == v.shape[0] == n and out.shape == (n, H * dv) and state.shape[1:] == (H, dk, dv)
+    assert q.shape[0] == k.shape[0] == v.shape[0] == n and out.shape == (n, H * dv) and state.shape[1:] == (H, dv, dk)
     for t in (q, k, v, out):
         assert t.stride(1) == 1
     _contig(state, "state"); _i32(slot_of_row, "slot_of_row"); _i32(cu_q, "cu_q")

@@ -1,6 +1,7 @@
 """Mixers with a decaying matrix state per head (linear attention).  Per request and head
 
     S_t = diag(a_t) S_(t-1) + k_t v_t^T        S: [dim, vdim], fp32, zero at the request's start
+                                               (kept transposed, [vdim, dim], in the request's state slot)
     o_t = S_t^T q_t
 
 `lightning_attention`: q, k, v = silu(h W), a_t one constant factor per head; the heads' outputs are
@@ -24,7 +25,8 @@ from .base import Mixer, StateNeed, WeightDecl, register_mixer
 
 class _LinearAttention(Mixer):
     def cache_need(self):
-        return StateNeed(shape=(self.H, self.dk, self.dv), dtype="float32")
+        # S transposed, [value column][key channel]: a thread of the kernel owns channels of one column
+        return StateNeed(shape=(self.H, self.dv, self.dk), dtype="float32")
 
     def _project(self, h, w):
         out = torch.empty((h.shape[0], w.shape[0]), dtype=self.act_dtype, device=h.device)
