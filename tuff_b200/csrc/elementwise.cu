@@ -194,12 +194,12 @@ rmsnorm_fork_rows_kernel(const float* s_in, const float* __restrict__ w, float e
     pdl_launch_dependents();
     if (r >= n_rows) return;
     const float* sr = s_in + (size_t)r * d;
-    float4 v[RMS_VEC];
+    float4 v[RMS_VEC], g[RMS_VEC];                 // the row and the weights: all loads in flight before the sum
     float ss = 0.f;
 #pragma unroll
     for (int i = 0; i < RMS_VEC; ++i) {
         const int k = (i * 32 + lane) * 4;
-        if (k < d) v[i] = __ldcg(reinterpret_cast<const float4*>(sr + k));
+        if (k < d) { v[i] = __ldcg(reinterpret_cast<const float4*>(sr + k)); g[i] = *reinterpret_cast<const float4*>(w + k); }
     }
 #pragma unroll
     for (int i = 0; i < RMS_VEC; ++i) {
@@ -215,8 +215,7 @@ rmsnorm_fork_rows_kernel(const float* s_in, const float* __restrict__ w, float e
     for (int i = 0; i < RMS_VEC; ++i) {
         const int k = (i * 32 + lane) * 4;
         if (k < d) {
-            const float4 g = *reinterpret_cast<const float4*>(w + k);
-            const float a = v[i].x * scale * g.x, b = v[i].y * scale * g.y, c = v[i].z * scale * g.z, e = v[i].w * scale * g.w;
+            const float a = v[i].x * scale * g[i].x, b = v[i].y * scale * g[i].y, c = v[i].z * scale * g[i].z, e = v[i].w * scale * g[i].w;
             const size_t o = (size_t)r * d + k;
             if (x_out) *reinterpret_cast<float4*>(x_out + o) = make_float4(a, b, c, e);
             if (s_out) *reinterpret_cast<float4*>(s_out + o) = make_float4(alpha * a, alpha * b, alpha * c, alpha * e);
